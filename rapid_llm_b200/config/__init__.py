@@ -2,6 +2,7 @@
 
 from .engine_config import EngineConfig, parse_dtype
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .basitar import BasitarConfig
 from .kopatar import KopatarConfig
 from .mezadra import MezadraConfig
 from .qwen3 import Qwen3Config
@@ -16,8 +17,10 @@ from .registry import (
 register_architecture(Qwen3Config)
 register_architecture(KopatarConfig)
 register_architecture(MezadraConfig)
+register_architecture(BasitarConfig)
 
 __all__ = [
+    "BasitarConfig",
     "EngineConfig",
     "KopatarConfig",
     "LayerSpec",

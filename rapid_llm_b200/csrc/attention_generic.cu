@@ -23,13 +23,13 @@ constexpr int kGenericMaxD = 256;
 template <typename T>
 __global__ void attention_generic_kernel(
     const T* __restrict__ q,            // [tokens, hq, d]
-    const T* __restrict__ cache,        // [num_pages, 2, hkv, page_size, d]
+    const T* __restrict__ cache,        // [num_pages, kv_planes (2, or 1: values are the keys' rows), hkv, page_size, d]
     T* __restrict__ out,                // [tokens, hq, d]
     const int* __restrict__ positions,  // [tokens]
     const int* __restrict__ token_slot, // [tokens]
     const int* __restrict__ block_table,  // [slots, max_pages]
     int tokens, int hq, int hkv, int d, int page_size, int num_pages, int max_pages, int slots,
-    int window, float scale, float softcap, const float* __restrict__ sink, int* __restrict__ fault) {
+    int window, float scale, float softcap, const float* __restrict__ sink, int kv_planes, int* __restrict__ fault) {
   __shared__ float q_staged[kGenericWarps][kGenericMaxD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * kGenericWarps + warp;
@@ -54,7 +54,8 @@ __global__ void attention_generic_kernel(
 
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
   const size_t head_stride = static_cast<size_t>(page_size) * d;
-  const size_t v_offset = static_cast<size_t>(hkv) * head_stride;  // K plane -> V plane
+  // K plane -> V plane; a cache of one plane keeps rows that are keys and values at once
+  const size_t v_offset = kv_planes == 2 ? static_cast<size_t>(hkv) * head_stride : 0;
 
   float running_max = -INFINITY, running_sum = 0.0f;
   float acc[kGenericMaxD / 32];
@@ -72,7 +73,7 @@ __global__ void attention_generic_kernel(
         atomicOr(fault, kFaultPageId);
       } else {
         k_row = static_cast<long long>(
-            ((static_cast<size_t>(page) * 2 * hkv + kv_head) * page_size + (j % page_size)) * d);
+            ((static_cast<size_t>(page) * kv_planes * hkv + kv_head) * page_size + (j % page_size)) * d);
         const T* kr = cache + k_row;
         float dot = 0.0f;
         for (int i = 0; i < d; i += 8) {
@@ -128,11 +129,11 @@ extern "C" int rl_attention_generic(int dtype, const void* q, const void* cache,
                                     const int* positions, const int* token_slot,
                                     const int* block_table, int tokens, int hq, int hkv, int d,
                                     int page_size, int num_pages, int max_pages, int slots,
-                                    int window, float scale, float softcap, const float* sink, int* fault,
-                                    cudaStream_t stream) {
+                                    int window, float scale, float softcap, const float* sink, int kv_planes,
+                                    int* fault, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (d <= 0 || d % 16 != 0 || d > rl::kGenericMaxD || hkv <= 0 || hq % hkv != 0 ||
-      page_size <= 0 || window < 0 || softcap < 0.0f)
+      page_size <= 0 || window < 0 || softcap < 0.0f || kv_planes < 1 || kv_planes > 2)
     return static_cast<int>(cudaErrorInvalidValue);
   const long long items = static_cast<long long>(tokens) * hq;
   const unsigned blocks =
@@ -141,7 +142,7 @@ extern "C" int rl_attention_generic(int dtype, const void* q, const void* cache,
     rl::attention_generic_kernel<scalar_t><<<blocks, rl::kGenericWarps * 32, 0, stream>>>(
         static_cast<const scalar_t*>(q), static_cast<const scalar_t*>(cache),
         static_cast<scalar_t*>(out), positions, token_slot, block_table, tokens, hq, hkv, d,
-        page_size, num_pages, max_pages, slots, window, scale, softcap, sink, fault);
+        page_size, num_pages, max_pages, slots, window, scale, softcap, sink, kv_planes, fault);
   });
   return rl::launch_status();
 }

@@ -72,6 +72,8 @@ struct AttentionArgs {
   float scale;              // the plain scale (used with softcap)
   float softcap;            // 0 = scores are not squashed
   const float* sink;        // null = no sink
+  int kv_planes;            // 2; or 1 for a cache [num_pages, 1, hkv, page_size, D] whose rows are keys and values at once
+                            // (the mma.sync tiles only)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -167,7 +169,7 @@ attention_mma_kernel(const AttentionArgs args) {
   const int k_end = min(hi, k_begin + per_split);
   const int n_blocks = k_end > k_begin ? (k_end - k_begin + kBlockN - 1) / kBlockN : 0;
   const int* table = args.block_table + static_cast<size_t>(bad ? 0 : slot) * args.max_pages;
-  const size_t v_plane = static_cast<size_t>(args.hkv) * args.page_size * kD;
+  const size_t v_plane = args.kv_planes == 2 ? static_cast<size_t>(args.hkv) * args.page_size * kD : 0;
 
   // The page ids of this item's key range, fetched once and side by side (a lookup per
   // 16-byte copy would put a dependent global load in front of every copy).  The block table
@@ -219,7 +221,7 @@ attention_mma_kernel(const AttentionArgs args) {
     copy_page[i] = regular && small_pages ? r / args.page_size : 0;
     copy_src[i] = (regular && small_pages ? r % args.page_size : r) * kD + c * 8;
   }
-  const size_t page_stride = static_cast<size_t>(2) * args.hkv * args.page_size * kD;
+  const size_t page_stride = static_cast<size_t>(args.kv_planes) * args.hkv * args.page_size * kD;
   const bf16* head_base = args.cache + static_cast<size_t>(kv_head) * args.page_size * kD;
 
   auto load_block = [&](int stage, int kb) {
@@ -729,12 +731,19 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
                      const int* entry_slot, const int* block_table, int tokens, int hq, int hkv,
                      int head_dim, int page_size, int num_pages, int max_pages, int slots,
                      int window, int splits, float scale, int* fault, int pdl, int decode_kernel, int decode_rows,
-                     int chunk_rows, int decode_splits, float softcap, const float* sink, cudaStream_t stream) {
+                     int chunk_rows, int decode_splits, float softcap, const float* sink, int kv_planes,
+                     cudaStream_t stream) {
   if (tokens == 0 || (n_chunk_items == 0 && n_decode_items == 0)) return 0;
   const bool plain_scores = !(softcap > 0.0f) && sink == nullptr;
   if (!plain_scores) {          // squashed scores and sinks: the tcgen05 chunk tiles and the mma.sync tiles take them
     if (softcap < 0.0f || (decode_splits > 0 && decode_splits != splits)) return static_cast<int>(cudaErrorInvalidValue);
     decode_kernel = 1;
+  }
+  if (kv_planes == 1) {         // rows that are keys and values at once: the mma.sync tiles read them, the tcgen05 tiles do not
+    if (chunk_rows == attn::kPfRows || (decode_splits > 0 && decode_splits != splits)) return static_cast<int>(cudaErrorInvalidValue);
+    decode_kernel = 1;
+  } else if (kv_planes != 2) {
+    return static_cast<int>(cudaErrorInvalidValue);
   }
   if (head_dim != attn::kD || hkv <= 0 || hq % hkv != 0 || page_size <= 0 || window < 0 ||
       splits < 1 || (splits > 1 && (part_out == nullptr || part_lse == nullptr)) ||
@@ -760,7 +769,7 @@ int rl_attention_mma(const void* q, const void* cache, void* out, float* part_ou
   args.max_pages = max_pages; args.slots = slots; args.window = window; args.splits = splits;
   args.scale_log2 = scale * 1.4426950408889634f;
   args.fault = fault;
-  args.scale = scale; args.softcap = softcap; args.sink = sink;
+  args.scale = scale; args.softcap = softcap; args.sink = sink; args.kv_planes = kv_planes;
   int status = 0;
   bool merged_in_cluster = false;
   if (n_chunk_items > 0) {
@@ -886,7 +895,7 @@ int rl_attention_mma_static_scratch(const void* q, const void* cache, void* out,
   }
   return rl_attention_mma(q, cache, out, part_out, part_lse, chunk_items, n_chunk_items, decode_items,
                           n_decode_items, cu_seqlens, entry_start, entry_slot, block_table, tokens, hq, hkv,
-                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, 64, 0, 0.0f, nullptr, stream);
+                          head_dim, page_size, num_pages, max_pages, slots, window, splits, scale, fault, 0, 1, 0, 64, 0, 0.0f, nullptr, 2, stream);
 }
 
 }  // extern "C"

@@ -91,6 +91,16 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&out)[8]) {
   }
 }
 
+// The entry of a step's packed batch that row t belongs to: the last e with cu_seqlens[e] <= t.
+__device__ __forceinline__ int entry_of(const int* __restrict__ cu_seqlens, int entries, int t) {
+  int lo = 0, hi = entries - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu_seqlens[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
 // ---- programmatic dependent launch -------------------------------------------------------

@@ -65,6 +65,63 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
   }
 }
 
+// ------------------------------------------------------------ token + token-pair + position rows
+// out[t] = table[id] + pair_table[row] + position_table[p], a float32 sum that also opens the residual stream.
+// The pair's row is (previous id * mul_prev + id * mul_cur) mod buckets; a request's first token has no previous
+// one and takes row `buckets`, the table's last.  The previous id of a row is the row before it in the same entry;
+// for an entry's first row it is the id the request's slot keeps in `last_token`, which that same block then
+// brings up to date (the entry's last id), so that no other block touches the slot's word.
+template <typename T>
+__global__ void embedding_sum_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ table,
+                                     const T* __restrict__ pair_table, const T* __restrict__ position_table,
+                                     const int* __restrict__ ids, const int* __restrict__ feedback, int feedback_rows,
+                                     const int* __restrict__ positions, const int* __restrict__ cu_seqlens,
+                                     const int* __restrict__ entry_slot, int entries, int* last_token, int slots,
+                                     int hidden, int vocab, int buckets, long long mul_prev, long long mul_cur,
+                                     int max_positions, int* __restrict__ fault) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  auto id_of = [&](int row) {
+    int id = ids[row];
+    if (id < 0 && feedback != nullptr && -(id + 1) < feedback_rows) id = feedback[-(id + 1)];
+    if (id < 0 || id >= vocab) {
+      if (threadIdx.x == 0) atomicOr(fault, kFaultTokenId);
+      id = 0;
+    }
+    return id;
+  };
+  const int e = entry_of(cu_seqlens, entries, t);
+  const int first = cu_seqlens[e], last = cu_seqlens[e + 1] - 1;
+  int slot = entry_slot[e];
+  const bool slot_ok = slot >= 0 && slot < slots;
+  int pos = positions[t];
+  if (pos < 0 || pos >= max_positions) {
+    if (threadIdx.x == 0) atomicOr(fault, kFaultPosition);
+    pos = 0;
+  }
+  if (!slot_ok && threadIdx.x == 0) atomicOr(fault, kFaultSlot);
+  const int id = id_of(t);
+  long long row = buckets;
+  if (pos > 0) {
+    const int before = t > first ? id_of(t - 1) : (slot_ok ? last_token[slot] : 0);
+    row = (before * mul_prev + id * mul_cur) % buckets;
+    if (row < 0) row += buckets;
+  }
+  __syncthreads();      // every thread has read the kept id before one of them replaces it
+  if (t == first && slot_ok && threadIdx.x == 0) last_token[slot] = id_of(last);
+  const T* a = table + static_cast<size_t>(id) * hidden;
+  const T* b = pair_table + static_cast<size_t>(row) * hidden;
+  const T* c = position_table + static_cast<size_t>(pos) * hidden;
+  T* dst = out + static_cast<size_t>(t) * hidden;
+  float* sr = stream ? stream + static_cast<size_t>(t) * hidden : nullptr;
+  pdl_wait();
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = to_float(a[i]) + to_float(b[i]) + to_float(c[i]);
+    if (sr) sr[i] = v;
+    dst[i] = from_float<T>(v);
+  }
+}
+
 // ------------------------------------------------------------ add + RMSNorm
 // One block per output row.  Row i of the output reads input row `row_index[i]`
 // (or i when row_index is null).
@@ -76,6 +133,9 @@ __global__ void embedding_kernel(T* __restrict__ out, const T* __restrict__ tabl
 //   mode 4: the norm sits on a sublayer's output: y = x * rsqrt(mean(x^2) + eps) * weight joins the
 //           stream, residual += y (stored), and out = the new residual rounded to the engine's dtype,
 //           which is what the next sublayer reads
+//   mode 5: as mode 4, and then the norm in front of the next sublayer at once: out = the new residual
+//           * rsqrt(mean(residual^2) + eps) * extra_vector, where `extra_vector` is that second norm's weight
+//           (no addend goes with this mode)
 // With `write_residual` the sum is stored back to `residual` (float32).
 // `extra_rows` (a row per token, the dtype of x) and `extra_vector` (float32, one row for all
 // tokens), where given, are added to r in that order before it is stored or normed: what a model
@@ -121,13 +181,13 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] += extra[i];
       }
-      if (extra_vector) {
+      if (extra_vector && mode != 5) {
         float extra[8];
         load8(extra_vector + at, extra);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] += extra[i];
       }
-      if (write_residual && mode != 4) store8(rr + at, v);
+      if (write_residual && mode < 4) store8(rr + at, v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) sum_sq += v[i] * v[i];
     }
@@ -136,14 +196,29 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
     if (active) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = v[i] * inv_rms * w[i];
-      if (mode == 4) {
+      if (mode >= 4) {
         float r[8];
         load8(rr + at, r);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] += r[i];
         store8(rr + at, v);
       }
-      store8(o + at, v);
+      if (mode != 5) store8(o + at, v);
+    }
+    if (mode == 5) {
+      float again = 0.0f;
+      if (active) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) again += v[i] * v[i];
+      }
+      again = block_sum(again, scratch);
+      const float inv_next = rsqrtf(again / static_cast<float>(hidden) + eps);
+      if (active) {
+        load8(extra_vector + at, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = v[i] * inv_next * w[i];
+        store8(o + at, v);
+      }
     }
   } else {
     pdl_wait();
@@ -152,8 +227,8 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
       float v = mode == 3 ? rr[i] : to_float(xr[i]);
       if (mode == 1) v += rr[i];
       if (er) v += to_float(er[i]);
-      if (extra_vector) v += extra_vector[i];
-      if (write_residual && mode != 4) rr[i] = v;
+      if (extra_vector && mode != 5) v += extra_vector[i];
+      if (write_residual && mode < 4) rr[i] = v;
       row_values[i] = v;
       sum_sq += v * v;
     }
@@ -161,11 +236,19 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
     const float inv_rms = rsqrtf(sum_sq / static_cast<float>(hidden) + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
       float v = row_values[i] * inv_rms * weight[i];
-      if (mode == 4) {
+      if (mode >= 4) {
         v += rr[i];
         rr[i] = v;
       }
-      o[i] = from_float<TOut>(v);
+      if (mode == 5) row_values[i] = v; else o[i] = from_float<TOut>(v);
+    }
+    if (mode == 5) {
+      float again = 0.0f;
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x) again += row_values[i] * row_values[i];
+      again = block_sum(again, scratch);
+      const float inv_next = rsqrtf(again / static_cast<float>(hidden) + eps);
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        o[i] = from_float<TOut>(row_values[i] * inv_next * extra_vector[i]);
     }
   }
 }
@@ -275,13 +358,32 @@ int rl_embedding(int dtype, void* out, const void* table, const int* ids, const 
   return 0;
 }
 
+int rl_embedding_sum(int dtype, void* out, float* stream_out, const void* table, const void* pair_table,
+                     const void* position_table, const int* ids, const int* feedback, int feedback_rows,
+                     const int* positions, const int* cu_seqlens, const int* entry_slot, int entries, int* last_token,
+                     int slots, int rows, int hidden, int vocab, int buckets, long long mul_prev, long long mul_cur,
+                     int max_positions, int* fault, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (entries < 1 || buckets < 1 || hidden < 1) return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    const int threads = hidden >= 2048 ? 256 : 128;
+    return rl::launch_kernel(rl::embedding_sum_kernel<scalar_t>, dim3(rows), dim3(threads), 0, stream, false,
+                             static_cast<scalar_t*>(out), stream_out, static_cast<const scalar_t*>(table),
+                             static_cast<const scalar_t*>(pair_table), static_cast<const scalar_t*>(position_table),
+                             ids, feedback, feedback_rows, positions, cu_seqlens, entry_slot, entries, last_token, slots,
+                             hidden, vocab, buckets, mul_prev, mul_cur, max_positions, fault);
+  });
+  return 0;
+}
+
 // x and out are `dtype`; residual and weight are float32.
 int rl_add_rmsnorm(int dtype, const void* x, float* residual, const float* weight, void* out,
                    const int* row_index, int rows, int hidden, float eps, int mode,
                    int write_residual, const void* extra_rows, const float* extra_vector, int pdl,
                    cudaStream_t stream) {
   if (rows == 0) return 0;
-  if (mode < 0 || mode > 4 || ((mode == 1 || mode >= 3) && residual == nullptr) ||
+  if (mode < 0 || mode > 5 || ((mode == 1 || mode >= 3) && residual == nullptr) ||
+      (mode == 5 && (extra_vector == nullptr || extra_rows != nullptr)) ||
       (write_residual && residual == nullptr) || hidden <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
   const bool vector = hidden % 8 == 0 && hidden <= 8 * 1024 && rl::aligned16(x) && rl::aligned16(out) &&

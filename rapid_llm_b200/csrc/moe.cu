@@ -59,7 +59,8 @@ template <typename T>
 __global__ void __launch_bounds__(kRouterWarps * 32)
 router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hidden, int experts,
                    int gates, int top, int* __restrict__ ids, float* __restrict__ weights,
-                   float* __restrict__ gate_out, float* __restrict__ scores_out, int tokens, int wide) {
+                   float* __restrict__ gate_out, float* __restrict__ scores_out, int tokens, int wide,
+                   const float* __restrict__ bias, int weigh) {
   extern __shared__ float moe_scores[];      // [kRouterTokens][rows] logits, then [kRouterWarps][kRouterTokens][rows] parts
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,7 +134,8 @@ router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hi
 #pragma unroll
     for (int part = 0; part < kRouterWarps; ++part) total += parts[part * kRouterTokens * rows + idx];
     // the logit: the choice is made on it (sigmoid keeps the order, and does not saturate into ties)
-    moe_scores[idx] = total;
+    const int row = idx % rows;
+    moe_scores[idx] = total + ((bias && row < experts) ? bias[row] : 0.0f);
   }
   __syncthreads();
   if (warp >= kRouterTokens || t0 + warp >= tokens) return;
@@ -159,10 +161,21 @@ router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hi
     if (best_e == 0x7fffffff) best_e = 0;      // every logit left is not a number: keep the index inside the table
     if (lane == 0) {
       ids[static_cast<size_t>(t) * top + j] = best_e;
-      weights[static_cast<size_t>(t) * top + j] = moe_sigmoid(best);
+      weights[static_cast<size_t>(t) * top + j] = weigh == 1 ? best : moe_sigmoid(best);
       s[best_e] = -INFINITY;      // taken
     }
     __syncwarp();
+  }
+  if (weigh == 1 && lane == 0) {
+    // the weights are the softmax over the chosen logits alone; the first chosen is the largest
+    float* w = weights + static_cast<size_t>(t) * top;
+    const float largest = w[0];
+    float sum = 0.0f;
+    for (int j = 0; j < top; ++j) {
+      w[j] = expf(w[j] - largest);
+      sum += w[j];
+    }
+    for (int j = 0; j < top; ++j) w[j] = w[j] / sum;
   }
 }
 
@@ -590,7 +603,7 @@ grouped_linear_wide_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bflo
 // ------------------------------------------------------------------ combine
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T* shared, const float* __restrict__ gate,
-                                   int gate_stride, T* __restrict__ out, int tokens, int hidden) {
+                                   int gate_stride, T* __restrict__ out, int tokens, int hidden, const float* weights) {
   pdl_trigger();
   pdl_wait();
   const long long total = static_cast<long long>(tokens) * hidden;
@@ -599,7 +612,11 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T
     const long long t = idx / hidden;
     const int c = static_cast<int>(idx - t * hidden);
     float sum = 0.0f;
-    for (int j = 0; j < top; ++j) sum += y[(t * top + j) * hidden + c];
+    if (weights) {
+      for (int j = 0; j < top; ++j) sum = fmaf(weights[t * top + j], y[(t * top + j) * hidden + c], sum);
+    } else {
+      for (int j = 0; j < top; ++j) sum += y[(t * top + j) * hidden + c];
+    }
     if (shared) sum += (gate ? gate[t * gate_stride] : 1.0f) * to_float(shared[idx]);
     out[idx] = from_float<T>(sum);
   }
@@ -612,10 +629,13 @@ extern "C" {
 int rl_moe_tile_rows(int wide) { return wide ? rl::kMoeWideM : rl::kMoeTileM; }
 
 int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int hidden, int experts, int gates, int top,
-                   int* ids, float* weights, float* gate_out, float* scores_out, int tokens, int pdl,
-                   cudaStream_t stream) {
+                   int* ids, float* weights, float* gate_out, float* scores_out, int tokens, const float* bias,
+                   int weigh, int pdl, cudaStream_t stream) {
+  // bias: one float per expert added to its logit, or null.  weigh 0: a chosen expert's weight is the sigmoid of its
+  // logit; 1: the softmax over the chosen logits.
   if (tokens == 0) return 0;
-  if (experts < 1 || top < 1 || top > experts || gates < 0 || (gates > 0 && gate_out == nullptr) || hidden < 1)
+  if (experts < 1 || top < 1 || top > experts || gates < 0 || (gates > 0 && gate_out == nullptr) || hidden < 1 ||
+      weigh < 0 || weigh > 1)
     return static_cast<int>(cudaErrorInvalidValue);
   const size_t smem = static_cast<size_t>(rl::kRouterTokens) * (rl::kRouterWarps + 1) * (experts + gates) * sizeof(float);
   if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
@@ -631,7 +651,7 @@ int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int h
     return rl::launch_kernel(rl::router_topk_kernel<scalar_t>,
                              dim3((tokens + rl::kRouterTokens - 1) / rl::kRouterTokens), dim3(rl::kRouterWarps * 32),
                              smem, stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, w, hidden, experts,
-                             gates, top, ids, weights, gate_out, scores_out, tokens, wide);
+                             gates, top, ids, weights, gate_out, scores_out, tokens, wide, bias, weigh);
   });
   return 0;
 }
@@ -711,8 +731,9 @@ int rl_grouped_linear(int dtype, const void* a, int a_stride, const void* w, con
                            pair_weight, top, by_token, n, k, static_cast<float*>(out_act), out_y);
 }
 
+// weights: one float per (token, choice) that multiplies the choice's row in the sum, or null.
 int rl_moe_combine(int dtype, const float* y, int top, const void* shared, const float* gate, int gate_stride,
-                   void* out, int tokens, int hidden, int pdl, cudaStream_t stream) {
+                   void* out, int tokens, int hidden, const float* weights, int pdl, cudaStream_t stream) {
   if (tokens == 0) return 0;
   const long long total = static_cast<long long>(tokens) * hidden;
   long long blocks = (total + 255) / 256;
@@ -720,7 +741,7 @@ int rl_moe_combine(int dtype, const float* y, int top, const void* shared, const
   RL_DISPATCH_DTYPE(dtype, {
     return rl::launch_kernel(rl::moe_combine_kernel<scalar_t>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream,
                              pdl != 0, y, top, static_cast<const scalar_t*>(shared), gate, gate_stride,
-                             static_cast<scalar_t*>(out), tokens, hidden);
+                             static_cast<scalar_t*>(out), tokens, hidden, weights);
   });
   return 0;
 }

@@ -24,16 +24,6 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : lo
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
-// The entry that owns packed row t: the last e with cu_seqlens[e] <= t.
-__device__ __forceinline__ int entry_of(const int* __restrict__ cu_seqlens, int entries, int t) {
-  int lo = 0, hi = entries - 1;
-  while (lo < hi) {
-    const int mid = (lo + hi + 1) >> 1;
-    if (cu_seqlens[mid] <= t) lo = mid; else hi = mid - 1;
-  }
-  return lo;
-}
-
 constexpr int kMaxTaps = 16;
 
 // ------------------------------------------------------------ short causal convolution
@@ -253,6 +243,76 @@ __global__ void decay_gate_kernel(const T* x, int x_stride, int col0, const floa
   }
 }
 
+// ------------------------------------------------------------ decay from a double exponential
+// decay[t, c] = exp(-exp(x[t, c] + bias[c])), float32: a decay per token and channel that stays inside (0, 1).
+template <typename T>
+__global__ void exp_decay_kernel(const T* x, int x_stride, int col0, const float* __restrict__ bias,
+                                 float* __restrict__ decay, int tokens, int C) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = static_cast<long long>(tokens) * C;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / C;
+    const int c = static_cast<int>(idx - t * C);
+    const float v = to_float(x[static_cast<size_t>(t) * x_stride + col0 + c]) + (bias ? bias[c] : 0.0f);
+    decay[idx] = expf(-expf(v));
+  }
+}
+
+// ------------------------------------------------------------ tanh of rows, in the rows' own type
+// out[i] = tanh(x[i]) in float32, rounded once: the activation between the two halves of a low-rank product.
+template <typename T>
+__global__ void tanh_rows_kernel(const T* x, T* out, long long total) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[idx] = from_float<T>(tanhf(to_float(x[idx])));
+}
+
+// ------------------------------------------------------------ blends of a row with the row before it
+// out[s][t][c] = x[t][c] + (before[t][c] - x[t][c]) * mu[s][c] for `mixes` vectors mu, float32 arithmetic, one
+// rounding at the store; out is `mixes` planes of [tokens, C].  `before` is the request's previous row: row t - 1 of
+// the same entry, the slot's kept row (float32) for the entry's first row, zeros at position 0.  The block of an
+// entry's first row also brings the kept row up to date (the entry's last row), each thread after it has read
+// what it needs; no other block touches the slot's row.
+template <typename T>
+__global__ void shift_mix_kernel(const T* x, int x_stride, const float* __restrict__ mu, int mixes, T* out,
+                                 float* kept, long long kept_stride, int kept_off,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ entry_slot,
+                                 const int* __restrict__ entry_start, int entries, int tokens, int C, int slots,
+                                 int* __restrict__ fault) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int e = entry_of(cu_seqlens, entries, t);
+  const int first = cu_seqlens[e], last = cu_seqlens[e + 1] - 1;
+  int slot = entry_slot[e];
+  const bool slot_ok = slot >= 0 && slot < slots;
+  if (!slot_ok) {
+    if (threadIdx.x == 0) atomicOr(fault, kFaultSlot);
+    slot = 0;
+  }
+  const bool opens = t == first;
+  const bool from_kept = opens && entry_start[e] > 0;
+  float* kr = kept + slot * kept_stride + kept_off;
+  const T* xr = x + static_cast<size_t>(t) * x_stride;
+  const T* pr = xr - x_stride;
+  const T* lr = x + static_cast<size_t>(last) * x_stride;
+  const size_t plane = static_cast<size_t>(tokens) * C;
+  pdl_wait();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float now = to_float(xr[c]);
+    float before = 0.0f;
+    if (from_kept) before = kr[c];
+    else if (!opens) before = to_float(pr[c]);
+    if (opens && slot_ok) kr[c] = to_float(lr[c]);
+    const float step = before - now;
+    for (int s = 0; s < mixes; ++s)
+      out[s * plane + static_cast<size_t>(t) * C + c] = from_float<T>(fmaf(step, mu[static_cast<size_t>(s) * C + c], now));
+  }
+}
+
 // ------------------------------------------------------------ unit vectors per head, write strengths
 // Heads of `dim` floats, `heads` of them side by side from column col0 of a float32 row: each becomes
 // x / sqrt(sum(x^2) + eps) times scale_low (heads below `split`) or scale_high.  One warp a head.
@@ -372,6 +432,9 @@ __global__ void rotate_heads_kernel(const T* in, int in_stride, int q_col0, int 
 //   u = beta * (v - S^T k)          with beta (the delta rule), else u = v_scale * v (v_scale may be null)
 //   S <- S + k u^T
 //   out = S^T q (+ skip * v)
+// With `bonus` (one number per head and row of S) the read-out comes first and the token's own pair enters it
+// weighed, before the state decays and takes the pair:
+//   out = (S + diag(bonus) k v^T)^T q;   S <- decay * S + k v^T
 // Query/key head of head h is h / (heads / kv_heads).
 //
 // A block owns (entry, head, a tile of columns of S) and walks the entry's tokens in order.  A column
@@ -388,6 +451,7 @@ struct ScanArgs {
   const float* beta;
   const float* v_scale;
   const float* skip;
+  const float* bonus;   // [heads, dim] or null: the read-out comes before the update and weighs the token's own pair
   float* out; int out_stride;
   float* state; long long state_stride; int state_off;
   const int* cu_seqlens; const int* entry_slot; const int* entry_start;
@@ -528,6 +592,11 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArg
     }
   }
 
+  float bonus[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+    bonus[r] = (a.bonus && row0 + r < a.dim) ? a.bonus[static_cast<size_t>(head) * a.dim + row0 + r] : 0.0f;
+
   int flip = 0;
   for (int base = 0; base < length; base += run, flip ^= 1) {
     const int count = min(run, length - base);
@@ -570,6 +639,34 @@ __global__ void __launch_bounds__(kScanThreads) linear_scan_kernel(const ScanArg
           qq[r] = q4.x; qq[r + 1] = q4.y; qq[r + 2] = q4.z; qq[r + 3] = q4.w;
         }
         const float vj = vp[g * tile_cols];
+        if (a.bonus) {
+          // read the state as the tokens before left it, the token's own pair weighed by the bonus; then decay and add
+          float gg[kRows];
+          if (a.decay_mode == 2) {
+#pragma unroll
+            for (int r = 0; r < kRows; r += 4) {
+              const float4 g4 = *reinterpret_cast<const float4*>(gp + g * dim_padded + r);
+              gg[r] = g4.x; gg[r + 1] = g4.y; gg[r + 2] = g4.z; gg[r + 3] = g4.w;
+            }
+          } else {
+            const float d = sdecay[tt + g];
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) gg[r] = d;
+          }
+          const float uj = sbeta[tt + g] * vj;
+          float even = 0.0f, odd = 0.0f;
+#pragma unroll
+          for (int r = 0; r < kRows; r += 2) {
+            const float kv0 = kk[r] * uj, kv1 = kk[r + 1] * uj;
+            even += (S[r] + bonus[r] * kv0) * qq[r];
+            odd += (S[r + 1] + bonus[r + 1] * kv1) * qq[r + 1];
+            S[r] = S[r] * gg[r] + kv0;
+            S[r + 1] = S[r + 1] * gg[r + 1] + kv1;
+          }
+          o[g] = even + odd;
+          vv[g] = vj;
+          continue;
+        }
         if (a.decay_mode == 2) {
 #pragma unroll
           for (int r = 0; r < kRows; r += 4) {
@@ -877,6 +974,41 @@ int rl_decay_gate(int dtype, const void* x, int x_stride, int col0, const float*
   return 0;
 }
 
+int rl_exp_decay(int dtype, const void* x, int x_stride, int col0, const float* bias, float* decay, int tokens,
+                 int channels, int pdl, cudaStream_t stream) {
+  if (tokens == 0 || channels == 0) return 0;
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::exp_decay_kernel<scalar_t>,
+                             dim3(rl::flat_blocks(static_cast<long long>(tokens) * channels, 256)), dim3(256), 0, stream,
+                             pdl != 0, static_cast<const scalar_t*>(x), x_stride, col0, bias, decay, tokens, channels);
+  });
+  return 0;
+}
+
+int rl_tanh_rows(int dtype, const void* x, void* out, long long total, int pdl, cudaStream_t stream) {
+  if (total == 0) return 0;
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::tanh_rows_kernel<scalar_t>, dim3(rl::flat_blocks(total, 256)), dim3(256), 0, stream,
+                             pdl != 0, static_cast<const scalar_t*>(x), static_cast<scalar_t*>(out), total);
+  });
+  return 0;
+}
+
+int rl_shift_mix(int dtype, const void* x, int x_stride, const float* mu, int mixes, void* out, float* kept,
+                 long long kept_stride, int kept_off, const int* cu_seqlens, const int* entry_slot,
+                 const int* entry_start, int entries, int tokens, int channels, int slots, int* fault, int pdl,
+                 cudaStream_t stream) {
+  if (tokens == 0 || channels == 0) return 0;
+  if (mixes < 1 || entries < 1) return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::shift_mix_kernel<scalar_t>, dim3(tokens), dim3(channels >= 1024 ? 256 : 128), 0, stream,
+                             pdl != 0, static_cast<const scalar_t*>(x), x_stride, mu, mixes, static_cast<scalar_t*>(out),
+                             kept, kept_stride, kept_off, cu_seqlens, entry_slot, entry_start, entries, tokens, channels,
+                             slots, fault);
+  });
+  return 0;
+}
+
 int rl_unit_heads(int dtype, float* rows, int stride, int col0, int heads, int dim, float eps, int split,
                   float scale_low, float scale_high, const void* gate_in, int gate_stride, int gate_col0, int gates,
                   float* gate_out, int tokens, int pdl, cudaStream_t stream) {
@@ -907,12 +1039,12 @@ int rl_rotate_heads(int dtype, const void* in, int in_stride, int q_col0, int k_
 
 int rl_linear_scan(const float* q, int q_stride, const float* k, int k_stride, const float* v, int v_stride,
                    const float* decay, int decay_mode, const float* beta, const float* v_scale, const float* skip,
-                   float* out, int out_stride, float* state, long long state_stride, int state_off,
+                   const float* bonus, float* out, int out_stride, float* state, long long state_stride, int state_off,
                    const int* cu_seqlens, const int* entry_slot, const int* entry_start, int entries, int heads,
                    int kv_heads, int dim, int vdim, int slots, int* fault, int pdl, cudaStream_t stream) {
   if (entries == 0) return 0;
   if (heads < 1 || kv_heads < 1 || heads % kv_heads || dim < 1 || dim > 1024 || vdim < 1 || decay_mode < 0 ||
-      decay_mode > 2 || decay == nullptr)
+      decay_mode > 2 || decay == nullptr || (bonus != nullptr && beta != nullptr))
     return static_cast<int>(cudaErrorInvalidValue);
   // rows a lane holds: few, so that a column's work spreads over many lanes; as many lanes a column as it takes
   const int rows = dim <= 32 ? 4 : (dim <= 256 ? 8 : (dim <= 512 ? 16 : 32));
@@ -920,7 +1052,7 @@ int rl_linear_scan(const float* q, int q_stride, const float* k, int k_stride, c
   while (partners * rows < dim) partners *= 2;
   rl::ScanArgs a;
   a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
-  a.decay = decay; a.decay_mode = decay_mode; a.beta = beta; a.v_scale = v_scale; a.skip = skip;
+  a.decay = decay; a.decay_mode = decay_mode; a.beta = beta; a.v_scale = v_scale; a.skip = skip; a.bonus = bonus;
   a.out = out; a.out_stride = out_stride; a.state = state; a.state_stride = state_stride; a.state_off = state_off;
   a.cu_seqlens = cu_seqlens; a.entry_slot = entry_slot; a.entry_start = entry_start;
   a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.slots = slots; a.partners = partners;

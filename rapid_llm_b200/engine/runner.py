@@ -364,6 +364,8 @@ class ModelRunner:
             group, pages = self.storage.entry_pages(position, entry.cache_from)
             state = self.storage.states[position]
             caches.append(LayerCache(group=group, pages=pages, writes=entry.cache_from is None, state=state))
+        for state in self.storage.states[len(caches):]:      # the embedding's, if it keeps one
+            caches.append(LayerCache(state=state))
         return caches
 
     @torch.no_grad()

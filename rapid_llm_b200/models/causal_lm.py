@@ -32,6 +32,7 @@ class CausalLM:
         if hasattr(self.head, "tie_to"):
             self.head.tie_to(self.embedding)
         # a learned row per pass of a looped run of layers, for run orders whose entries open passes
+        self._tensor_owner: dict | None = None
         self.pass_offset = None if spec.pass_offset is None else EMBEDDINGS.build(spec.pass_offset, **context)
         if self.device.type == "cuda":
             self._build_kernels()
@@ -70,11 +71,15 @@ class CausalLM:
         return specs
 
     def load_tensor(self, full_name: str, tensor: torch.Tensor) -> None:
-        for prefix, part in self._owners():
-            if full_name.startswith(prefix):
-                part.load_tensor(full_name[len(prefix):], tensor)
-                return
-        raise KeyError(full_name)
+        """Hand a tensor to the part that lists it (prefixes may be empty or begin alike, so a name is looked up
+        among the parts' own lists, not matched by its beginning)."""
+        if self._tensor_owner is None:
+            self._tensor_owner = {prefix + name: (part, name) for prefix, part in self._owners()
+                                  for name in part.tensor_specs()}
+        if full_name not in self._tensor_owner:
+            raise KeyError(full_name)
+        part, name = self._tensor_owner[full_name]
+        part.load_tensor(name, tensor)
 
     def finalize(self, loaded: set[str]) -> None:
         for prefix, part in self._owners():
@@ -100,7 +105,12 @@ class CausalLM:
         return needs
 
     def state_needs(self) -> list[StateNeed | None]:
-        return [self.layers[entry.layer].state_need() for entry in self.spec.schedule]
+        """One entry per position of the run order, and one more behind them if the embedding keeps a state
+        per request (what :meth:`forward` then expects as the last of ``caches``)."""
+        needs = [self.layers[entry.layer].state_need() for entry in self.spec.schedule]
+        if hasattr(self.embedding, "state_need"):
+            needs.append(self.embedding.state_need())
+        return needs
 
     def step_planners(self) -> list:
         """The distinct host-side planners of the layers (one per key)."""
@@ -114,11 +124,12 @@ class CausalLM:
     def forward(self, batch: StepBatch, caches: list[LayerCache]) -> torch.Tensor:
         """Logits ``[R, vocab]`` at ``batch.logit_rows``; runs only the tokens of the step."""
         batch.defer_products = True      # the queue is run below, before anything but a kernel reads a result
+        own = (caches[len(self.spec.schedule)],) if hasattr(self.embedding, "state_need") else ()
         if getattr(self.embedding, "opens_stream", False):
-            x, residual = self.embedding.forward_stream(batch)      # the float32 stream starts at the embedding
+            x, residual = self.embedding.forward_stream(batch, *own)      # the float32 stream starts at the embedding
             embedded = x
         else:
-            x = embedded = self.embedding.forward(batch)
+            x = embedded = self.embedding.forward(batch, *own)
             residual = None
         schedule = self.spec.schedule
         for position, entry in enumerate(schedule):

@@ -48,6 +48,7 @@ LIBRARIES: dict[str, list[str]] = {
     "gemm": ["gemm_bf16.cu", "gemm_chain.cu", "gemm_bf16_pair.cu"],
     "recurrent": ["recurrent.cu"],
     "moe": ["moe.cu"],
+    "latent": ["latent.cu"],
 }
 LIBRARY_FLAGS: dict[str, list[str]] = {}
 

@@ -133,7 +133,11 @@ def core() -> ctypes.CDLL:
         ]
         lib.rl_attention_generic.argtypes = [
             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p,
+            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p,
+        ]
+        lib.rl_embedding_sum.argtypes = [
+            c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+            c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
         ]
         lib.rl_gemm_f32.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.rl_sample.argtypes = [
@@ -141,7 +145,7 @@ def core() -> ctypes.CDLL:
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
         ]
         for name in (
-            "rl_embedding", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float", "rl_clamped_glu",
+            "rl_embedding", "rl_embedding_sum", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float", "rl_clamped_glu",
             "rl_rope_unit_write",
             "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample",
         ):
@@ -171,6 +175,33 @@ def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, fault: 
                             table.shape[1], table.shape[0], _ptr(fault), float(scale), _ptr(stream), 0, _stream()),   # first kernel of a step: an ordinary launch
         "embedding",
     )
+    return out
+
+
+def embedding_sum(out: torch.Tensor, stream: torch.Tensor | None, table: torch.Tensor, pair_table: torch.Tensor,
+                  position_table: torch.Tensor, batch, last_token: torch.Tensor, *, mul_prev: int, mul_cur: int) -> torch.Tensor:
+    """``out[t] = table[id_t] + pair_table[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] + position_table[p_t]``
+    as a float32 sum (also stored to ``stream`` if given); ``pair_table`` has ``buckets + 1`` rows and a request's first
+    token takes the last.  The id before an entry's first row is the one its slot keeps in ``last_token``
+    (int32 ``[slots, 1]``), brought up to date here."""
+    _need_cuda(out, stream, table, pair_table, position_table, last_token)
+    _expect("stream", stream, torch.float32), _expect("last_token", last_token, torch.int32)
+    for name, tensor in (("out", out), ("stream", stream), ("table", table), ("pair_table", pair_table),
+                         ("position_table", position_table), ("last_token", last_token)):
+        _contig(name, tensor)
+    rows, hidden = out.shape
+    if (table.dtype != out.dtype or pair_table.dtype != out.dtype or position_table.dtype != out.dtype
+            or table.shape[1] != hidden or pair_table.shape[1] != hidden or position_table.shape[1] != hidden
+            or rows != batch.token_ids.numel() or (stream is not None and stream.shape != out.shape)
+            or last_token.numel() != last_token.shape[0] or pair_table.shape[0] < 2):
+        raise KernelError("embedding_sum: shapes or dtypes do not agree")
+    feedback = batch.feedback
+    _check(core().rl_embedding_sum(
+        dtype_tag(out.dtype), _ptr(out), _ptr(stream), _ptr(table), _ptr(pair_table), _ptr(position_table),
+        _ptr(batch.token_ids), _ptr(feedback), 0 if feedback is None else feedback.numel(), _ptr(batch.positions),
+        _ptr(batch.cu_seqlens), _ptr(batch.entry_slot), batch.num_entries, _ptr(last_token), last_token.shape[0], rows,
+        hidden, table.shape[0], pair_table.shape[0] - 1, int(mul_prev), int(mul_cur), position_table.shape[0],
+        _ptr(batch.fault), _stream()), "embedding_sum")
     return out
 
 
@@ -416,8 +447,8 @@ def attention_generic(
         raise KernelError("attention: q/out do not hold [tokens, heads, head_dim]")
     if cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, cache and out must share a dtype")
-    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
-        raise KernelError("attention: cache must be [pages, 2, kv_heads, page_size, head_dim]")
+    if cache.dim() != 5 or cache.shape[1] not in (1, 2) or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError("attention: cache must be [pages, 2 (or 1: values are the keys' rows), kv_heads, page_size, head_dim]")
     if head_dim % 16 or head_dim > 256:
         raise KernelError(f"attention: head_dim {head_dim} must be a multiple of 16 up to 256")
     _check(
@@ -425,7 +456,7 @@ def attention_generic(
             dtype_tag(q.dtype), _ptr(q), _ptr(cache), _ptr(out), _ptr(positions), _ptr(token_slot),
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3],
             cache.shape[0], block_table.shape[1], block_table.shape[0], int(window), float(scale),
-            float(softcap), _ptr(sink), _ptr(fault), _stream(),
+            float(softcap), _ptr(sink), int(cache.shape[1]), _ptr(fault), _stream(),
         ),
         f"attention_generic(head_dim={head_dim})",
     )
@@ -456,7 +487,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.rl_attention_mma.argtypes = [
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+            c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
         ]
         lib.rl_attention_mma.restype = c_int
         lib.rl_attention_decode_max_clusters.argtypes = [c_int]
@@ -549,8 +580,8 @@ def attention_mma(
     if q.dim() != 2 or q.shape[1] != width or out.shape != q.shape:
         raise KernelError("attention: q and out must be [tokens, heads * head_dim]")
     tokens = q.shape[0]
-    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
-        raise KernelError("attention: cache must be [pages, 2, kv_heads, page_size, head_dim]")
+    if cache.dim() != 5 or cache.shape[1] not in (1, 2) or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError("attention: cache must be [pages, 2 (or 1: values are the keys' rows), kv_heads, page_size, head_dim]")
     if num_heads % num_kv_heads:
         raise KernelError("attention: heads must be a multiple of kv heads")
     n_chunk = 0 if chunk_items is None else chunk_items.shape[0]
@@ -566,7 +597,7 @@ def attention_mma(
             _ptr(block_table), tokens, num_heads, num_kv_heads, head_dim, cache.shape[3], cache.shape[0],
             block_table.shape[1], block_table.shape[0], int(window), int(splits), float(scale),
             _ptr(fault), int(PDL), {"auto": 0, "mma": 1, "deep": 2, "shallow": 3}[decode_kernel], int(decode_rows), int(chunk_rows),
-            int(decode_splits), float(softcap), _ptr(sink), _stream(),
+            int(decode_splits), float(softcap), _ptr(sink), int(cache.shape[1]), _stream(),
         ),
         f"attention_mma(head_dim={head_dim})",
     )
@@ -923,16 +954,20 @@ def recurrent() -> ctypes.CDLL:
         lib.rl_rotate_heads.argtypes = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
         lib.rl_linear_scan.argtypes = [
-            c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
             c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
             c_int, c_int, c_void_p, c_int, c_void_p,
         ]
+        lib.rl_exp_decay.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.rl_tanh_rows.argtypes = [c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
+        lib.rl_shift_mix.argtypes = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int,
+                                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.rl_gated_norm.argtypes = [c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.rl_xielu.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p]
         lib.rl_scaled_sum.argtypes = [c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int, c_void_p]
         for name in ("rl_causal_conv_silu", "rl_activate_rows", "rl_decay_gate", "rl_unit_heads", "rl_rotate_heads", "rl_linear_scan",
-                     "rl_gated_norm", "rl_xielu", "rl_scaled_sum"):
+                     "rl_gated_norm", "rl_xielu", "rl_scaled_sum", "rl_exp_decay", "rl_tanh_rows", "rl_shift_mix"):
             getattr(lib, name).restype = c_int
         _RECURRENT_SET = True
     return lib
@@ -1051,20 +1086,24 @@ def rotate_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.T
 def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, out: torch.Tensor,
                 state: torch.Tensor, batch, *, heads: int, kv_heads: int, dim: int, vdim: int,
                 beta: torch.Tensor | None = None, v_scale: torch.Tensor | None = None,
-                skip: torch.Tensor | None = None) -> torch.Tensor:
+                skip: torch.Tensor | None = None, bonus: torch.Tensor | None = None) -> torch.Tensor:
     """The recurrence ``S <- decay * S; u = beta * (v - S^T k)`` (or ``v_scale * v`` without ``beta``);
     ``S <- S + k u^T; out = S^T q + skip * v`` per head over every entry's tokens, from and into
-    ``state [slots, heads * dim * vdim]`` (float32; a request at position 0 starts from zeros).
+    ``state [slots, heads * dim * vdim]`` (float32; a request at position 0 starts from zeros).  With ``bonus``
+    (float32 ``[heads, dim]``) the read-out comes first and weighs the token's own pair:
+    ``out = (S + diag(bonus) k v^T)^T q``, then ``S <- decay * S + k v^T``.
 
     All operands float32: ``q``, ``k`` ``[T, kv_heads * dim]`` and ``v`` ``[T, heads * vdim]`` (views of columns
     are fine), ``decay`` ``[heads]`` (fixed), ``[T, heads]`` or ``[T, heads * dim]`` (one per row of ``S``),
     ``beta``/``v_scale`` ``[T, heads]``, ``skip`` ``[heads]``, ``out`` ``[T, heads * vdim]``.
     """
-    _need_cuda(q, k, v, decay, out, state, beta, v_scale, skip)
+    _need_cuda(q, k, v, decay, out, state, beta, v_scale, skip, bonus)
     for name, tensor in (("q", q), ("k", k), ("v", v), ("decay", decay), ("out", out), ("beta", beta),
-                         ("v_scale", v_scale), ("skip", skip)):
+                         ("v_scale", v_scale), ("skip", skip), ("bonus", bonus)):
         _expect(name, tensor, torch.float32)
-    _contig("decay", decay), _contig("beta", beta), _contig("v_scale", v_scale), _contig("skip", skip)
+    _contig("decay", decay), _contig("beta", beta), _contig("v_scale", v_scale), _contig("skip", skip), _contig("bonus", bonus)
+    if bonus is not None and (bonus.numel() != heads * dim or beta is not None):
+        raise KernelError("linear_scan: bonus is [heads, dim] and does not go with beta")
     tokens = q.shape[0]
     if q.shape[1] != kv_heads * dim or k.shape != q.shape or v.shape != (tokens, heads * vdim) or out.shape != v.shape:
         raise KernelError("linear_scan: shapes of q, k, v and out do not agree")
@@ -1086,11 +1125,163 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.
     _check(
         recurrent().rl_linear_scan(
             _ptr(q), _row_stride("q", q), _ptr(k), _row_stride("k", k), _ptr(v), _row_stride("v", v), _ptr(decay), mode,
-            _ptr(beta), _ptr(v_scale), _ptr(skip), _ptr(out), _row_stride("out", out), _ptr(state), stride, 0,
+            _ptr(beta), _ptr(v_scale), _ptr(skip), _ptr(bonus), _ptr(out), _row_stride("out", out), _ptr(state), stride, 0,
             _ptr(batch.cu_seqlens), _ptr(batch.entry_slot), _ptr(batch.entry_start), batch.num_entries, heads, kv_heads,
             dim, vdim, slots, _ptr(batch.fault), int(early), _stream()),
         f"linear_scan(dim={dim}, vdim={vdim})",
     )
+    return out
+
+
+def exp_decay(x: torch.Tensor, bias: torch.Tensor | None, decay: torch.Tensor) -> torch.Tensor:
+    """``decay = exp(-exp(x + bias))`` as float32 ``[T, C]``; ``x`` may be a view of columns."""
+    _need_cuda(x, bias, decay)
+    _expect("bias", bias, torch.float32), _expect("decay", decay, torch.float32), _contig("bias", bias), _contig("decay", decay)
+    tokens, channels = x.shape
+    if decay.shape != (tokens, channels) or (bias is not None and bias.numel() != channels):
+        raise KernelError("exp_decay: shapes do not agree")
+    _check(recurrent().rl_exp_decay(dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), 0, _ptr(bias), _ptr(decay), tokens,
+                                    channels, int(PDL), _stream()), "exp_decay")
+    return decay
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = tanh(x)`` (float32 arithmetic, one rounding), both contiguous and of one dtype; may be in place."""
+    _need_cuda(x, out)
+    _contig("x", x), _contig("out", out)
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("tanh_rows: out must have the shape and dtype of x")
+    _check(recurrent().rl_tanh_rows(dtype_tag(x.dtype), _ptr(x), _ptr(out), x.numel(), int(PDL), _stream()), "tanh_rows")
+    return out
+
+
+def shift_mix(x: torch.Tensor, mu: torch.Tensor, out: torch.Tensor, kept: torch.Tensor, batch) -> torch.Tensor:
+    """``out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s]`` for each of the vectors ``mu [S, C]`` (float32), ``x[t - 1]``
+    the row before within the same request: the row before in this step, the request's kept row
+    (``kept [slots, C]`` float32, brought up to date here) at the start of a portion, zeros at position 0.
+    ``out`` is ``[S * T, C]`` of ``x``'s dtype, plane after plane."""
+    _need_cuda(x, mu, out, kept)
+    _expect("mu", mu, torch.float32), _contig("mu", mu), _contig("out", out)
+    tokens, channels = x.shape
+    mixes = mu.shape[0]
+    slots, stride = _state_row(kept)
+    if mu.shape != (mixes, channels) or out.shape != (mixes * tokens, channels) or out.dtype != x.dtype \
+            or kept.shape[1] != channels:
+        raise KernelError("shift_mix: shapes do not agree")
+    _check(recurrent().rl_shift_mix(dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), _ptr(mu), mixes, _ptr(out),
+                                    _ptr(kept), stride, 0, _ptr(batch.cu_seqlens), _ptr(batch.entry_slot),
+                                    _ptr(batch.entry_start), batch.num_entries, tokens, channels, slots,
+                                    _ptr(batch.fault), int(PDL), _stream()), "shift_mix")
+    return out
+
+
+_LATENT_LIB: ctypes.CDLL | None = None
+ROTATE_HALVES, ROTATE_NEIGHBOURS = 0, 1      # entry i with i + R / 2; entry 2i with 2i + 1
+
+
+def latent_lib() -> ctypes.CDLL:
+    global _LATENT_LIB
+    if _LATENT_LIB is None:
+        lib = load_library("latent")
+        lib.rl_latent_norm_write.argtypes = [
+            c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+            c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_void_p]
+        lib.rl_latent_rotate_queries.argtypes = [c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                                                 c_void_p, c_float, c_int, c_int, c_int, c_void_p]
+        lib.rl_sigmoid_scale_heads.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.rl_heads_linear.argtypes = [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_void_p]
+        for name in ("rl_latent_norm_write", "rl_latent_rotate_queries", "rl_sigmoid_scale_heads", "rl_heads_linear"):
+            getattr(lib, name).restype = c_int
+        _LATENT_LIB = lib
+    return _LATENT_LIB
+
+
+def latent_norm_write(down: torch.Tensor, *, q_col0: int, q_rank: int, c_col0: int, kv_rank: int, rot: int,
+                      q_weight: torch.Tensor, c_weight: torch.Tensor, eps: float, q_out: torch.Tensor, cache: torch.Tensor,
+                      kv_dest: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor | None, magnitude: float,
+                      layout: int, fault: torch.Tensor) -> None:
+    """From a row ``down[t]`` that holds a query latent (``q_rank`` numbers at ``q_col0``) and ``[c | key part]``
+    (``kv_rank + rot`` numbers at ``c_col0``): ``q_out[t]`` = RMS norm of the query latent times ``q_weight``; the
+    cache row ``kv_dest[t]`` of ``cache [pages, page_size, D]`` = ``[RMS norm of c times c_weight | the key part
+    rotated by the position | zeros]``.  float32 arithmetic, one rounding."""
+    _need_cuda(down, q_weight, c_weight, q_out, cache, kv_dest, positions, freq, fault)
+    _expect("q_weight", q_weight, torch.float32), _expect("c_weight", c_weight, torch.float32), _expect("freq", freq, torch.float32)
+    _expect("kv_dest", kv_dest, torch.int32), _expect("positions", positions, torch.int32)
+    _contig("q_out", q_out), _contig("cache", cache), _contig("freq", freq)
+    tokens, width = down.shape[0], cache.shape[-1]
+    if (q_out.shape != (tokens, q_rank) or q_out.dtype != down.dtype or cache.dtype != down.dtype
+            or q_weight.numel() != q_rank or c_weight.numel() != kv_rank or (rot and freq.numel() != rot // 2)
+            or q_col0 + q_rank > down.shape[1] or c_col0 + kv_rank + rot > down.shape[1] or kv_dest.numel() != tokens):
+        raise KernelError("latent_norm_write: shapes or dtypes do not agree")
+    _check(latent_lib().rl_latent_norm_write(
+        dtype_tag(down.dtype), _ptr(down), _row_stride("down", down), int(q_col0), int(q_rank), int(c_col0), int(kv_rank),
+        int(rot), _ptr(q_weight), _ptr(c_weight), float(eps), _ptr(q_out), _ptr(cache), _ptr(kv_dest),
+        cache.numel() // width, width, _ptr(positions), _ptr(freq), float(magnitude), int(layout), tokens, _ptr(fault),
+        int(PDL), _stream()), "latent_norm_write")
+
+
+def latent_rotate_queries(q: torch.Tensor, wide: torch.Tensor, *, heads: int, dim: int, rot: int, kv_rank: int,
+                          positions: torch.Tensor, freq: torch.Tensor | None, magnitude: float, layout: int) -> torch.Tensor:
+    """``q [T, heads * (dim + rot)]``: every head's last ``rot`` numbers, rotated by the position, go to columns
+    ``[kv_rank, kv_rank + rot)`` of the head's ``D`` columns of ``wide [T, heads * D]``; the columns behind get zeros."""
+    _need_cuda(q, wide, positions, freq)
+    _expect("freq", freq, torch.float32), _expect("positions", positions, torch.int32)
+    _contig("q", q), _contig("wide", wide), _contig("freq", freq)
+    tokens = q.shape[0]
+    if (q.shape[1] != heads * (dim + rot) or wide.shape[0] != tokens or wide.shape[1] % heads or wide.dtype != q.dtype
+            or (rot and freq.numel() != rot // 2)):
+        raise KernelError("latent_rotate_queries: shapes or dtypes do not agree")
+    _check(latent_lib().rl_latent_rotate_queries(
+        dtype_tag(q.dtype), _ptr(q), int(heads), int(dim), int(rot), _ptr(wide), int(kv_rank), wide.shape[1] // heads,
+        _ptr(positions), _ptr(freq), float(magnitude), int(layout), tokens, int(PDL), _stream()), "latent_rotate_queries")
+    return wide
+
+
+def sigmoid_scale_heads(rows: torch.Tensor, gate: torch.Tensor, *, heads: int) -> torch.Tensor:
+    """``rows[t, h, :] *= sigmoid(gate[t, h])`` in place; ``rows [T, heads * width]``, ``gate`` ``[T, >= heads]`` (a view
+    of columns is fine)."""
+    _need_cuda(rows, gate)
+    _contig("rows", rows)
+    if rows.shape[1] % heads or gate.shape[0] != rows.shape[0] or gate.shape[1] < heads or gate.dtype != rows.dtype:
+        raise KernelError("sigmoid_scale_heads: shapes or dtypes do not agree")
+    _check(latent_lib().rl_sigmoid_scale_heads(dtype_tag(rows.dtype), _ptr(rows), int(heads), rows.shape[1] // heads,
+                                               _ptr(gate), _row_stride("gate", gate), 0, rows.shape[0], int(PDL), _stream()),
+           "sigmoid_scale_heads")
+    return rows
+
+
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, x_col0: int = 0) -> torch.Tensor:
+    """A product per head: ``out[t, h, :N] = x[t, h, x_col0 : x_col0 + K] @ weight[h]^T`` with ``weight [heads, N, K]``,
+    ``x [T, heads * x_width]`` and ``out [T, heads * out_width]``; float32 sums (true 32-bit for float32 operands).
+    Columns of ``out`` behind ``N`` in each head are left as they are."""
+    _need_cuda(x, weight, out)
+    _contig("x", x), _contig("weight", weight), _contig("out", out)
+    heads, n_out, k = weight.shape
+    if (x.dtype != weight.dtype or out.dtype != x.dtype or x.shape[1] % heads or out.shape[1] % heads
+            or out.shape[0] != x.shape[0]):
+        raise KernelError("heads_linear: shapes or dtypes do not agree")
+    _check(latent_lib().rl_heads_linear(dtype_tag(x.dtype), _ptr(x), x.shape[1] // heads, int(x_col0), _ptr(weight), _ptr(out),
+                                        out.shape[1] // heads, x.shape[0], heads, n_out, k, int(PDL), _stream()),
+           "heads_linear")
+    return out
+
+
+def join_then_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, next_weight: torch.Tensor,
+                      out: torch.Tensor, eps: float) -> torch.Tensor:
+    """A norm on a sublayer's output and the norm in front of the next one in one pass over the row:
+    ``residual += x * rsqrt(mean(x^2) + eps) * weight`` (float32, in place), then
+    ``out = residual * rsqrt(mean(residual^2) + eps) * next_weight`` in the engine's dtype."""
+    _need_cuda(x, residual, weight, next_weight, out)
+    for name, tensor in (("weight", weight), ("next_weight", next_weight), ("residual", residual)):
+        _expect(name, tensor, torch.float32), _contig(name, tensor)
+    _contig("x", x), _contig("out", out)
+    if (residual.shape != x.shape or out.shape != x.shape or out.dtype != x.dtype or weight.numel() != x.shape[-1]
+            or next_weight.numel() != x.shape[-1]):
+        raise KernelError("join_then_rmsnorm: shapes of x, residual, the weights and out do not agree")
+    _check(core().rl_add_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), None,
+                                 x.shape[0], x.shape[1], float(eps), 5, 1, None, _ptr(next_weight), int(PDL), _stream()),
+           "join_then_rmsnorm")
     return out
 
 
@@ -1151,13 +1342,13 @@ def moe_lib() -> ctypes.CDLL:
     if _MOE_LIB is None:
         lib = load_library("moe")
         lib.rl_router_topk.argtypes = [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                       c_void_p, c_void_p, c_int, c_int, c_void_p]
+                                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         lib.rl_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.rl_moe_tile_rows.argtypes = [c_int]
         lib.rl_grouped_linear.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                           c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
-        lib.rl_moe_combine.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                       c_void_p]
+        lib.rl_moe_combine.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                                       c_int, c_void_p]
         for name in ("rl_router_topk", "rl_moe_plan", "rl_grouped_linear", "rl_moe_combine", "rl_moe_tile_rows"):
             getattr(lib, name).restype = c_int
         _MOE_LIB = lib
@@ -1180,10 +1371,15 @@ def moe_max_tiles(pairs: int, experts: int, wide: bool = False) -> int:
 
 
 def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int, ids: torch.Tensor,
-                weights: torch.Tensor, gates: torch.Tensor | None = None, scores: torch.Tensor | None = None) -> None:
-    """``s = sigmoid(weight[:experts] @ x[t])`` in float32; ``ids[t]``/``weights[t]`` the ``top`` largest (ties: the
-    lower index) with their ``s``; rows of ``weight`` behind the experts' are gates, ``gates[t, g] = sigmoid(.)``."""
-    _need_cuda(x, weight, ids, weights, gates, scores)
+                weights: torch.Tensor, gates: torch.Tensor | None = None, scores: torch.Tensor | None = None,
+                bias: torch.Tensor | None = None, softmax_chosen: bool = False) -> None:
+    """``z = weight[:experts] @ x[t] (+ bias)`` in float32; ``ids[t]`` the ``top`` largest (ties: the lower index),
+    ``weights[t]`` their ``sigmoid(z)``, or with ``softmax_chosen`` the softmax over the chosen ``z`` alone; rows of
+    ``weight`` behind the experts' are gates, ``gates[t, g] = sigmoid(.)``."""
+    _need_cuda(x, weight, ids, weights, gates, scores, bias)
+    _expect("bias", bias, torch.float32), _contig("bias", bias)
+    if bias is not None and bias.numel() != experts:
+        raise KernelError("router_topk: one bias per expert")
     _expect("weight", weight, torch.float32), _expect("ids", ids, torch.int32), _expect("weights", weights, torch.float32)
     _expect("gates", gates, torch.float32), _expect("scores", scores, torch.float32)
     _contig("weight", weight), _contig("ids", ids), _contig("weights", weights), _contig("gates", gates), _contig("scores", scores)
@@ -1193,7 +1389,8 @@ def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int
             or (extra > 0 and (gates is None or gates.shape != (tokens, extra))):
         raise KernelError("router_topk: shapes do not agree")
     _check(moe_lib().rl_router_topk(dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), _ptr(weight), hidden, experts, extra,
-                                    top, _ptr(ids), _ptr(weights), _ptr(gates), _ptr(scores), tokens, int(PDL), _stream()),
+                                    top, _ptr(ids), _ptr(weights), _ptr(gates), _ptr(scores), tokens, _ptr(bias),
+                                    int(bool(softmax_chosen)), int(PDL), _stream()),
            "router_topk")
 
 
@@ -1235,17 +1432,20 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, sorted_pairs: torch.Te
 
 
 def moe_combine(y: torch.Tensor, top: int, out: torch.Tensor, shared: torch.Tensor | None = None,
-                gate: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t])``, float32 sums in the order of ``j``."""
-    _need_cuda(y, out, shared, gate)
+                gate: torch.Tensor | None = None, weights: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = sum_j (weights[t, j] *) y[t * top + j] (+ gate[t] * shared[t])``, float32 sums in the order of ``j``."""
+    _need_cuda(y, out, shared, gate, weights)
+    _expect("weights", weights, torch.float32), _contig("weights", weights)
+    if weights is not None and weights.numel() != y.shape[0]:
+        raise KernelError("moe_combine: one weight per (token, choice)")
     _expect("y", y, torch.float32), _expect("gate", gate, torch.float32)
     _contig("y", y), _contig("out", out), _contig("shared", shared)
     tokens, hidden = out.shape
     if y.shape != (tokens * top, hidden) or (shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype)):
         raise KernelError("moe_combine: shapes do not agree")
     _check(moe_lib().rl_moe_combine(dtype_tag(out.dtype), _ptr(y), int(top), _ptr(shared), _ptr(gate),
-                                    0 if gate is None else _row_stride("gate", gate), _ptr(out), tokens, hidden, int(PDL),
-                                    _stream()), "moe_combine")
+                                    0 if gate is None else _row_stride("gate", gate), _ptr(out), tokens, hidden,
+                                    _ptr(weights), int(PDL), _stream()), "moe_combine")
     return out
 
 

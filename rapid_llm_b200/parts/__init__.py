@@ -1,6 +1,6 @@
 """Parts a layer is put together from; importing the package registers the built-in ones."""
 
-from . import attention, block, embedding, mlp, moe, norm, parallel, recurrent, rope  # noqa: F401  (registration)
+from . import attention, block, embedding, latent, mlp, moe, norm, parallel, recurrent, rope  # noqa: F401  (registration)
 from .base import (
     BLOCKS,
     EMBEDDINGS,

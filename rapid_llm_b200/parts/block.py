@@ -12,6 +12,9 @@ whether they accept (small steps in bfloat16 do).
 
 ``outnorm`` (:class:`OutputNormBlock`): ``h' = h + Norm(Mixer(h)); h'' = h' + Norm(FeedForward(h'))``.  The
 sublayers read the stream itself; the stream is the float32 ``residual`` and ``x`` its rounding.
+
+``sandwich`` (:class:`SandwichBlock`): a norm on both sides of each sublayer,
+``h' = h + NormB(Mixer(NormA(h))); h'' = h' + NormD(FeedForward(NormC(h')))``, the stream float32 in ``residual``.
 """
 
 from __future__ import annotations
@@ -162,3 +165,82 @@ class OutputNormBlock(PreNormBlock):
             gemm.flush()
             x = self.feed_forward_norm.join(wide, residual, batch)
         return x, residual
+
+
+class NormedStream:
+    """Rows that are already the leading norm's result of the stream: what a :class:`SandwichBlock` hands the next
+    one when the norm on its last sublayer's output took that block's first norm along."""
+
+    def __init__(self, rows: torch.Tensor) -> None:
+        self.rows = rows
+
+
+class _LeadingOffer:
+    """A :class:`SandwichBlock`'s first norm as the block before it sees it: only another sandwich block takes it
+    along (``norm``); as a norm that rides on a product it declines."""
+
+    def __init__(self, norm) -> None:
+        self.norm = norm
+
+    def following(self, residual, batch):
+        return None
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(PreNormBlock):
+    """A norm in front of and behind each sublayer: ``h <- h + NormB(Mixer(NormA(h)))``, then
+    ``h <- h + NormD(FeedForward(NormC(h)))``.  The stream lives in ``residual`` (float32, opened by the embedding
+    or from ``x``); the norm behind a sublayer adds its result there and, in the same kernel, forms the norm in front
+    of the next sublayer (of this block, or of the next block if that is a sandwich block too)."""
+
+    stream_in_residual = True
+    NAMES = {"mixer_norm": "norm1", "mixer_out_norm": "norm1b", "mixer": "mix.", "feed_forward_norm": "norm2",
+             "feed_forward_out_norm": "norm2b", "feed_forward": "mlp."}
+
+    def __init__(self, *, layer: LayerSpec, dtype, device, names: dict[str, str] | None = None) -> None:
+        super().__init__(layer=layer, dtype=dtype, device=device, names=names)
+        self.mixer_out_norm = NORMS.build(layer.norm, dtype=dtype, device=device)
+        self.feed_forward_out_norm = None
+        if self.feed_forward is not None:
+            self.feed_forward_out_norm = NORMS.build(layer.norm, dtype=dtype, device=device)
+        for norm in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward_out_norm):
+            if norm is not None and not hasattr(norm, "join_then"):
+                raise ValueError("the sandwich arrangement needs norms that can join the stream (kind 'rmsnorm')")
+
+    def _children(self):
+        children = [(self.names["mixer_norm"], self.mixer_norm), (self.names["mixer_out_norm"], self.mixer_out_norm),
+                    (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            children += [(self.names["feed_forward_norm"], self.feed_forward_norm),
+                         (self.names["feed_forward_out_norm"], self.feed_forward_out_norm),
+                         (self.names["feed_forward"], self.feed_forward)]
+        # the longest prefix first: "norm1b" must not be taken for "norm1" followed by "b"
+        return tuple(sorted(children, key=lambda child: -len(child[0])))
+
+    def leading_norm(self):
+        return _LeadingOffer(self.mixer_norm)
+
+    def _close(self, y, norm, residual, batch, then_norm):
+        """The norm behind a sublayer; with ``then_norm`` (an RMS norm) that norm of the new stream comes back."""
+        gemm.flush()
+        if then_norm is not None:
+            return NormedStream(norm.join_then(y, residual, then_norm, batch))
+        return norm.join(y, residual, batch)
+
+    def forward(self, x, residual, batch, cache, then_norm=None, addend=None):
+        if addend is not None or isinstance(x, ScaledRows):
+            raise ValueError("this arrangement takes plain rows and no addend")
+        after = then_norm.norm if isinstance(then_norm, _LeadingOffer) else None
+        if isinstance(x, NormedStream):
+            normed = x.rows
+        else:
+            if residual is None:       # the embedding did not open the stream: it starts as x
+                residual = batch.workspace.get("residual", x.shape[0], x.shape[1], torch.float32)
+                kernels.to_float(x, residual)
+            normed = self.mixer_norm.of_stream(residual, batch)
+        mixed = self.mixer.forward(normed, batch, cache)
+        if self.feed_forward is None:
+            return self._close(mixed, self.mixer_out_norm, residual, batch, after), residual
+        normed = self._close(mixed, self.mixer_out_norm, residual, batch, self.feed_forward_norm).rows
+        wide = self.feed_forward.forward(normed, batch)
+        return self._close(wide, self.feed_forward_out_norm, residual, batch, after), residual

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import gemm, kernels
-from .base import EMBEDDINGS, HEADS, MATRIX, VECTOR, Part, TensorSpec
+from .base import EMBEDDINGS, HEADS, MATRIX, VECTOR, Part, StateNeed, TensorSpec
 
 
 @EMBEDDINGS.register("token_embedding")
@@ -49,6 +49,61 @@ class TokenEmbedding(Part):
         out = batch.workspace.get("embedded", batch.num_tokens, self.hidden, self.dtype)
         stream = batch.workspace.get("residual", batch.num_tokens, self.hidden, torch.float32)
         kernels.embedding(out, self.weight, batch.token_ids, batch.fault, batch.feedback, scale=self.scale, stream=stream)
+        return out, stream
+
+
+@EMBEDDINGS.register("summed_embedding")
+class SummedEmbedding(TokenEmbedding):
+    """A token's row plus a row for the pair (previous token, token) plus a learned row for the position:
+    ``x_t = E[id_t] + B[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] + P[p_t]``, a float32 sum that opens the
+    residual stream.  ``B`` has ``buckets + 1`` rows; a request's first token, which has no previous one, takes the
+    last.  The request's latest token id is its state (one int32 per slot), so that a portion of a prompt or a single
+    decoded token finds the id before its first row."""
+
+    opens_stream = True
+
+    def __init__(self, *, vocab_size: int, hidden_size: int, pair_buckets: int, pair_mul_prev: int, pair_mul_cur: int,
+                 max_positions: int, dtype, device, name: str = "weight", pair_name: str = "pair",
+                 position_name: str = "positions") -> None:
+        super().__init__(vocab_size=vocab_size, hidden_size=hidden_size, dtype=dtype, device=device, name=name,
+                         opens_stream=True)
+        self.buckets, self.mul_prev, self.mul_cur = int(pair_buckets), int(pair_mul_prev), int(pair_mul_cur)
+        self.max_positions = int(max_positions)
+        if self.buckets < 1 or self.max_positions < 1:
+            raise ValueError("a summed embedding needs at least one pair bucket and one position")
+        self.pair_name, self.position_name = pair_name, position_name
+        self.pair = self.new_storage((self.buckets + 1, self.hidden), MATRIX)
+        self.positions = self.new_storage((self.max_positions, self.hidden), MATRIX)
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((1,), torch.int32)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.vocab, self.hidden)),
+                self.pair_name: TensorSpec((self.buckets + 1, self.hidden)),
+                self.position_name: TensorSpec((self.max_positions, self.hidden))}
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        if name == self.pair_name:
+            self.pair.copy_(tensor)
+        elif name == self.position_name:
+            self.positions.copy_(tensor)
+        else:
+            super().load_tensor(name, tensor)
+
+    def parameter_bytes(self) -> int:
+        return (self.weight.numel() + self.pair.numel() + self.positions.numel()) * self.weight.element_size()
+
+    def forward(self, batch, cache=None) -> torch.Tensor:
+        return self.forward_stream(batch, cache)[0]
+
+    def forward_stream(self, batch, cache=None) -> tuple[torch.Tensor, torch.Tensor]:
+        if cache is None or cache.state is None:
+            raise ValueError("the engine did not give this embedding the state row it asked for")
+        out = batch.workspace.get("embedded", batch.num_tokens, self.hidden, self.dtype)
+        stream = batch.workspace.get("residual", batch.num_tokens, self.hidden, torch.float32)
+        kernels.embedding_sum(out, stream, self.weight, self.pair, self.positions, batch, cache.state,
+                              mul_prev=self.mul_prev, mul_cur=self.mul_cur)
         return out, stream
 
 

@@ -7,6 +7,11 @@ up are linear, the kernels multiply the two products by ``s_e`` in float32 inste
 A shared expert of the same form (a :class:`~rapid_llm_b200.parts.mlp.SwiGLU` under ``shared.``) may run for
 every token; with ``shared_gate`` its result is multiplied by ``sigmoid(w_sg . x)``, one number per token.
 
+Two more options: ``router_bias`` adds a learned number per expert to ``z`` before the choice, and
+``weighting="softmax_chosen"`` makes the weights the softmax over the chosen ``z`` alone.  Without ``scale_input``
+the weight multiplies the expert's result instead, ``y = sum_e w_e Expert_e(x)``, in the float32 sum over a
+token's choices.
+
 The step's (token, expert) pairs are grouped by expert on the device (no host round trip, so a decode
 step is captured into a graph like any other), the two products run over the groups
 (``ops.kernels.grouped_linear``), and a last kernel sums a token's experts in the order of its choices.
@@ -28,6 +33,7 @@ class RoutedExperts(FeedForward):
                  shared_size: int | None = None, shared_gate: bool = False, scale_input: bool = True,
                  expert_prefix: str = "e", router_name: str = "router", shared_prefix: str = "shared.",
                  shared_gate_name: str = "sg", gate_name: str = "gate", up_name: str = "up", down_name: str = "down",
+                 router_bias: bool = False, router_bias_name: str = "router.b", weighting: str = "sigmoid",
                  dtype, device) -> None:
         super().__init__(dtype=dtype, device=device)
         self.hidden, self.experts, self.top, self.inter = int(hidden_size), int(num_experts), int(top_k), int(expert_size)
@@ -35,9 +41,11 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"top_k ({top_k}) must lie between 1 and the number of experts ({num_experts})")
         if shared_gate and not shared_size:
             raise ValueError("a shared gate needs a shared expert")
-        if not scale_input:
-            raise ValueError("weights on the experts' outputs are not built: the weight scales an expert's input")
-        self.scale_input = True
+        if weighting not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"unknown weighting {weighting!r}: 'sigmoid' or 'softmax_chosen'")
+        self.scale_input, self.softmax_chosen = bool(scale_input), weighting == "softmax_chosen"
+        self.router_bias_name = router_bias_name
+        self.bias = self.new_storage((self.experts,), VECTOR) if router_bias else None
         self.expert_prefix, self.router_name = expert_prefix, router_name
         self.shared_prefix, self.shared_gate_name = shared_prefix, shared_gate_name
         self.part_names = (gate_name, up_name, down_name)
@@ -61,6 +69,8 @@ class RoutedExperts(FeedForward):
             specs[prefix + up] = TensorSpec((self.inter, self.hidden))
             specs[prefix + down] = TensorSpec((self.hidden, self.inter))
         specs[self.router_name] = TensorSpec((self.experts, self.hidden), VECTOR)
+        if self.bias is not None:
+            specs[self.router_bias_name] = TensorSpec((self.experts,), VECTOR)
         if self.shared is not None:
             for name, spec in self.shared.tensor_specs().items():
                 specs[self.shared_prefix + name] = spec
@@ -72,6 +82,9 @@ class RoutedExperts(FeedForward):
         gate, up, down = self.part_names
         if name == self.router_name:
             self.router[: self.experts].copy_(tensor.to(torch.float32))
+            return
+        if self.bias is not None and name == self.router_bias_name:
+            self.bias.copy_(tensor.to(torch.float32))
             return
         if self.shared is not None and name.startswith(self.shared_prefix):
             rest = name[len(self.shared_prefix):]
@@ -114,7 +127,8 @@ class RoutedExperts(FeedForward):
         ids = space.get("moe_ids", tokens, top, i32)
         weights = space.get("moe_weights", tokens, top, f32)
         gates = space.get("moe_gates", tokens, 1, f32) if self.has_gate else None
-        kernels.router_topk(x, self.router, experts=experts, top=top, ids=ids, weights=weights, gates=gates)
+        kernels.router_topk(x, self.router, experts=experts, top=top, ids=ids, weights=weights, gates=gates,
+                            bias=self.bias, softmax_chosen=self.softmax_chosen)
         order = space.get("moe_sorted", tokens, top, i32).view(-1)
         place = space.get("moe_place", tokens, top, i32).view(-1)
         wide = kernels.moe_wide_takes(x.dtype, self.hidden, self.inter)      # the pipelined bfloat16 tiles
@@ -123,9 +137,10 @@ class RoutedExperts(FeedForward):
         max_tiles = kernels.moe_plan(ids, experts, order, place, meta, batch.fault, wide=wide)
         act = space.get("moe_act", tokens, top * self.inter, x.dtype).view(pairs, self.inter)
         kernels.grouped_linear(x, self.gate_up, order, meta, top=top, by_token=True, max_tiles=max_tiles,
-                               pair_weight=weights.view(-1), out_act=act, wide=wide)
+                               pair_weight=weights.view(-1) if self.scale_input else None, out_act=act, wide=wide)
         each = space.get("moe_each", tokens, top * self.hidden, f32).view(pairs, self.hidden)
         kernels.grouped_linear(act, self.down, order, meta, top=top, by_token=False, max_tiles=max_tiles, out_y=each, wide=wide)
         shared = None if self.shared is None else self.shared.forward(x, batch)
         out = space.get("moe_out", tokens, self.hidden, x.dtype)
-        return kernels.moe_combine(each, top, out, shared=shared, gate=gates)
+        return kernels.moe_combine(each, top, out, shared=shared, gate=gates,
+                                   weights=None if self.scale_input else weights.view(-1))

@@ -1,7 +1,8 @@
 """RMSNorm with the residual add folded in.
 
 ``y = r * rsqrt(mean(r^2) + eps) * w`` with ``r = x`` or ``r = x + residual``; the weight
-multiplies as ``w`` (not ``1 + w``).  Formula and the fused residual are the reference's
+multiplies as ``w`` (with ``unit_offset`` the checkpoint stores ``w - 1``, a weight around zero, and one is added
+when it is loaded).  Formula and the fused residual are the reference's
 (``rapid_llm/kernels/ops/layernorm/skip_rmsnorm.py:41-48,51-85``; CPU twin
 ``rapid_llm/kernels/backend/cpu.py:18-29``); here the residual stream stays float32.
 """
@@ -20,20 +21,23 @@ FIRST, ADD, PLAIN = 0, 1, 2
 class RMSNorm(Norm):
     reads_deferred = True       # it launches through ops.kernels, which runs queued products first
 
-    def __init__(self, *, size: int, eps: float, dtype, device, name: str = "weight") -> None:
+    def __init__(self, *, size: int, eps: float, dtype, device, name: str = "weight", unit_offset: bool = False) -> None:
         super().__init__(dtype=dtype, device=device)
         self.size = int(size)
         self.eps = float(eps)
         self.name = name          # the tensor's name after the part's prefix (may be empty)
+        self.unit_offset = bool(unit_offset)
         self.weight = self.new_storage((self.size,), VECTOR)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
-        return {self.name: TensorSpec((self.size,), VECTOR, init="ones_normal")}
+        return {self.name: TensorSpec((self.size,), VECTOR, init="normal" if self.unit_offset else "ones_normal")}
 
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
         if name != self.name:
             raise KeyError(name)
         self.weight.copy_(tensor.to(torch.float32))
+        if self.unit_offset:
+            self.weight.add_(1.0)        # float32: the sum of one and a 16-bit number is exact enough to be the weight
 
     def parameter_bytes(self) -> int:
         return self.weight.numel() * 4
@@ -52,6 +56,11 @@ class RMSNorm(Norm):
         engine's dtype (what the next sublayer reads)."""
         out = batch.workspace.get(name, y.shape[0], self.size, y.dtype)
         return kernels.join_rmsnorm(y, residual, self.weight, out, self.eps)
+
+    def join_then(self, y, residual, next_norm: "RMSNorm", batch, name="normed"):
+        """:meth:`join`, and ``next_norm`` of the new stream in the same pass: returns that norm's result."""
+        out = batch.workspace.get(name, y.shape[0], self.size, y.dtype)
+        return kernels.join_then_rmsnorm(y, residual, self.weight, next_norm.weight, out, self.eps)
 
     def of_stream(self, residual, batch, *, row_index=None, name="normed"):
         """The norm of the float32 stream itself (rows picked by ``row_index``), in the engine's dtype."""

@@ -1,6 +1,6 @@
 """Mixers that carry a state of fixed size per request: linear recurrences over a matrix ``S``.
 
-All three keep, per head, a float32 matrix ``S`` of ``key_dim x value_dim`` in the request's state row
+All of them keep, per head, a float32 matrix ``S`` of ``key_dim x value_dim`` in the request's state row
 and advance it token by token in one kernel (``ops.kernels.linear_scan``), which serves portions of
 prompts and single decoded tokens alike:
 
@@ -10,6 +10,9 @@ prompts and single decoded tokens alike:
   ``S <- gamma S + k v^T; o = S^T q``, queries and keys rotated by position.
 * :class:`Lightning` (``lightning``) — the same recurrence with SiLU on q, k and v, no rotation, and one norm
   over the heads side by side: ``S <- gamma S + k v^T; o = S^T q``.
+* :class:`ShiftedDecay` (``wkv``) — a decay per token, head and key channel computed from the input, every
+  projection reading a blend of the token's row with the row before it, and a bonus for the token's own pair:
+  ``o = (S + diag(u) k v^T)^T r; S <- diag(w) S + k v^T``.
 * :class:`StateSpaceDual` (``state_space_dual``) — the selective state space in its recurrent form:
   ``S <- exp(-exp(A) dt) S + dt B x^T; y = S^T C + D x``.
 
@@ -405,3 +408,100 @@ class StateSpaceDual(_Recurrent):
         kernels.gated_norm(read, normed, group=inner // self.norm_groups, gate=proj[:, :inner], act=kernels.GATE_SILU,
                            gate_first=True, weight=self.norm, eps=self.eps)
         return gemm.linear(normed, self.o, space.get("ssd_out", rows, self.hidden, x.dtype), batch.fault)
+
+
+@MIXERS.register("wkv")
+class ShiftedDecay(_Recurrent):
+    """Linear attention whose projections read blends with the row before, with a decay made from the input.
+
+    With ``x'`` the request's previous row (zeros for its first token) each of r, k, v, g, w reads a blend of its own,
+    ``x + (x' - x) * mu_s``.  ``r, k, v = W_r, W_k, W_v`` of their blends (``num_heads`` heads of ``key_dim``; values
+    have the keys' size), ``gate = SiLU(W_g .)``, and the decay per head and key channel is
+    ``w = exp(-exp(W_w2 tanh(W_w1 .) + w0))``.  Per head ``o = (S + diag(u) k v^T)^T r`` and then
+    ``S <- diag(w) S + k v^T``: the bonus ``u`` weighs the token's own pair in its own read-out only.  Every head's
+    read-out is divided by its root mean square; the heads side by side are multiplied by ``norm`` (a weight per
+    column) and by the gate, then projected.  The blends' arithmetic, the decay, the state and the read-out are
+    float32; the request's last row is kept, in float32, behind ``S`` in its state row.
+    """
+
+    DEFAULT_NAMES = ("mu.r", "mu.k", "mu.v", "mu.g", "mu.w", "r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o")
+    BLENDS = ("r", "k", "v", "g", "w")
+
+    def __init__(self, *, hidden_size: int, num_heads: int, key_dim: int, decay_rank: int, norm_eps: float,
+                 names: dict[str, str] | None = None, dtype, device) -> None:
+        super().__init__(dtype=dtype, device=device)
+        self._set_names(names)
+        self.hidden, self.h, self.dim, self.rank = int(hidden_size), int(num_heads), int(key_dim), int(decay_rank)
+        self.eps = float(norm_eps)
+        self.c = self.h * self.dim
+        self.state_size, self.tail_size = self.h * self.dim * self.dim, self.hidden
+        self.mu = self.new_storage((len(self.BLENDS), self.hidden), VECTOR)
+        self.w_rkvg = self.new_storage((4, self.c, self.hidden), MATRIX)
+        self.w1 = self.new_storage((self.rank, self.hidden), MATRIX)
+        self.w2 = self.new_storage((self.c, self.rank), MATRIX)
+        self.w0 = self.new_storage((self.c,), VECTOR)
+        self.bonus = self.new_storage((self.h, self.dim), VECTOR)
+        self.norm = self.new_storage((self.c,), VECTOR)
+        self.o = self.new_storage((self.hidden, self.c), MATRIX)
+
+    def _tensors(self):
+        return (self.mu, self.w_rkvg, self.w1, self.w2, self.w0, self.bonus, self.norm, self.o)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        specs = {f"mu.{which}": TensorSpec((self.hidden,), VECTOR) for which in self.BLENDS}
+        for which in ("r", "k", "v", "g"):
+            specs[which] = TensorSpec((self.c, self.hidden))
+        specs.update({
+            "w1": TensorSpec((self.rank, self.hidden)), "w2": TensorSpec((self.c, self.rank)),
+            "w0": TensorSpec((self.c,), VECTOR), "u": TensorSpec((self.h, self.dim), VECTOR),
+            "norm": TensorSpec((self.c,), VECTOR, init="ones_normal"), "o": TensorSpec((self.hidden, self.c)),
+        })
+        return self._named(specs)
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        name = self._ours.get(name, "")
+        f32 = torch.float32
+        if name.startswith("mu.") and name[3:] in self.BLENDS:
+            self.mu[self.BLENDS.index(name[3:])].copy_(tensor.to(f32))
+        elif name in ("r", "k", "v", "g"):
+            self.w_rkvg["rkvg".index(name)].copy_(tensor)
+        elif name == "w1":
+            self.w1.copy_(tensor)
+        elif name == "w2":
+            self.w2.copy_(tensor)
+        elif name == "o":
+            self.o.copy_(tensor)
+        elif name == "w0":
+            self.w0.copy_(tensor.to(f32))
+        elif name == "u":
+            self.bonus.copy_(tensor.to(f32))
+        elif name == "norm":
+            self.norm.copy_(tensor.to(f32))
+        else:
+            raise KeyError(name)
+
+    def workspace_elements_per_token(self) -> int:
+        return 5 * self.hidden + 4 * self.c + 2 * (4 * self.c) + 2 * self.rank + self.hidden
+
+    def forward(self, x, batch, cache):
+        rows, space, f32, c = x.shape[0], batch.workspace, torch.float32, self.c
+        S, kept = self._state_views(cache)
+        blends = kernels.shift_mix(x, self.mu, space.get("wkv_blends", 5 * rows, self.hidden, x.dtype), kept, batch)
+        proj = space.get("wkv_proj", 4 * rows, c, x.dtype)               # planes r | k | v | g
+        for index in range(4):
+            gemm.linear(blends[index * rows : (index + 1) * rows], self.w_rkvg[index],
+                        proj[index * rows : (index + 1) * rows], batch.fault)
+        low = gemm.linear(blends[4 * rows :], self.w1, space.get("wkv_low", rows, self.rank, x.dtype), batch.fault)
+        gemm.flush()
+        kernels.tanh_rows(low, low)
+        high = gemm.linear(low, self.w2, space.get("wkv_high", rows, c, x.dtype), batch.fault)
+        gemm.flush()
+        decay = kernels.exp_decay(high, self.w0, space.get("wkv_decay", rows, c, f32))
+        rkv = kernels.activate_rows(proj[: 3 * rows], space.get("wkv_rkv", 3 * rows, c, f32), act=False)
+        read = space.get("wkv_read", rows, c, f32)
+        kernels.linear_scan(rkv[:rows], rkv[rows : 2 * rows], rkv[2 * rows :], decay, read, S, batch, heads=self.h,
+                            kv_heads=self.h, dim=self.dim, vdim=self.dim, bonus=self.bonus)
+        normed = space.get("wkv_normed", rows, c, x.dtype)
+        kernels.gated_norm(read, normed, group=self.dim, gate=proj[3 * rows :], act=kernels.GATE_SILU, weight=self.norm,
+                           eps=self.eps)
+        return gemm.linear(normed, self.o, space.get("wkv_out", rows, self.hidden, x.dtype), batch.fault)

@@ -69,6 +69,34 @@ class RotaryFrequencies(PositionEncoding):
         self.rotary_dim, self.theta, self.max_positions = int(rotary_dim), float(theta), int(max_positions)
         exponents = torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / max(self.rotary_dim, 1)
         self.inv_freq = (float(theta) ** -exponents).to(torch.float32).to(self.device)
+        self.magnitude = 1.0       # what cosine and sine are multiplied by
 
     def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
         raise ValueError("this position encoding has no tables; its kernel computes the angles")
+
+
+@POSITION_ENCODINGS.register("yarn_frequencies")
+class YarnFrequencies(RotaryFrequencies):
+    """Frequencies stretched for contexts longer than the ``original`` one: the slow ones divided by ``factor``, the
+    fast ones kept, a linear ramp in between.  With ``d(t) = R ln(original / (2 pi t)) / (2 ln theta)`` the index
+    at which a frequency turns ``t`` times over the original context, ``lo = max(floor(d(fast)), 0)``,
+    ``hi = min(ceil(d(slow)), R - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, the frequency is
+    ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``; cosine and sine are multiplied by ``0.1 ln(factor) + 1``."""
+
+    def __init__(self, *, rotary_dim: int, theta: float, max_positions: int, factor: float, original: float,
+                 fast: float, slow: float, dtype, device) -> None:
+        super().__init__(rotary_dim=rotary_dim, theta=theta, max_positions=max_positions, dtype=dtype, device=device)
+        import math
+
+        size = self.rotary_dim
+
+        def turns_at(turns: float) -> float:
+            return size * math.log(float(original) / (2.0 * math.pi * float(turns))) / (2.0 * math.log(float(theta)))
+
+        lo = max(math.floor(turns_at(fast)), 0)
+        hi = min(math.ceil(turns_at(slow)), size - 1)
+        index = torch.arange(size // 2, dtype=torch.float64)
+        ramp = ((index - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        plain = float(theta) ** -(torch.arange(0, size, 2, dtype=torch.float64) / max(size, 1))
+        self.inv_freq = (plain / float(factor) * ramp + plain * (1.0 - ramp)).to(torch.float32).to(self.device)
+        self.magnitude = 0.1 * math.log(float(factor)) + 1.0
