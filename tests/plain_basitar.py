@@ -159,9 +159,13 @@ def router_choice(h, weights, prefix, top):
     return order, torch.softmax(chosen, dim=-1), logits
 
 
-def routed_feed_forward(h, weights, prefix, mlp):
+def routed_feed_forward(h, weights, prefix, mlp, margins=None):
     experts, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    order, share, _ = router_choice(h, weights, prefix, top)
+    order, share, logits = router_choice(h, weights, prefix, top)
+    if margins is not None and top < experts:
+        # how clearly the last chosen expert beats the first one left out, in units of the logits' spread
+        ranked = torch.sort(logits, dim=-1, descending=True).values
+        margins.append(float(((ranked[:, top - 1] - ranked[:, top]) / logits.std()).min()))
     out = torch.zeros_like(h)
     for e in range(experts):
         name = f"{prefix}e{e}."
@@ -185,8 +189,9 @@ def run_mixer(kind, h, weights, prefix, sizes, eps):
     raise ValueError(kind)
 
 
-def forward(tokens, weights, config, return_layers=False):
-    """Logits ``[T, vocab]`` (float64) of a whole sequence; with ``return_layers`` also the stream after every layer."""
+def forward(tokens, weights, config, return_layers=False, margins=None):
+    """Logits ``[T, vocab]`` (float64) of a whole sequence; with ``return_layers`` also the stream after every layer.
+    ``margins`` (a list) receives the narrowest router decision of every routed layer."""
     eps = float(config["norm"]["eps"])
     x = embed(tokens, weights, config)
     streams = []
@@ -197,8 +202,24 @@ def forward(tokens, weights, config, return_layers=False):
         mlp = layer.get("mlp")
         if mlp is not None:
             h = offset_norm(x, _w(weights, p + "norm2"), eps)
-            wide = dense_feed_forward(h, weights, p + "mlp.") if mlp["kind"] == "dense" else routed_feed_forward(h, weights, p + "mlp.", mlp)
+            wide = dense_feed_forward(h, weights, p + "mlp.") if mlp["kind"] == "dense" else routed_feed_forward(h, weights, p + "mlp.", mlp, margins)
             x = x + offset_norm(wide, _w(weights, p + "norm2b"), eps)
         streams.append(x)
     logits = offset_norm(x, _w(weights, "final.norm"), eps) @ _w(weights, "embed").T
     return (logits, torch.stack(streams)) if return_layers else logits
+
+
+def greedy(tokens, weights, config, steps: int) -> list[int]:
+    """The ``steps`` tokens that always taking the largest logit produces after ``tokens``."""
+    tokens = list(tokens)
+    start = len(tokens)
+    for _ in range(steps):
+        tokens.append(int(forward(tokens, weights, config)[-1].argmax()))
+    return tokens[start:]
+
+
+def clear_margin(tokens, weights, config) -> float:
+    """The narrowest router decision of the sequence (infinite for a model without routers)."""
+    margins: list = []
+    forward(tokens, weights, config, margins=margins)
+    return min(margins) if margins else math.inf
