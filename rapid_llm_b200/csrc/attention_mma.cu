@@ -112,7 +112,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // kWarpsM warps stacked over the tile's rows, kWarpsN warps side by side over each block's keys.
-template <int kWarpsM, int kWarpsN, int kStages>
+// kShared: the cache has one plane, a row is key and value at once, and a block's rows are brought to shared
+// memory once and read as both (half the copies, half the stages' memory, so two CTAs fit on an SM at any head size).
+template <int kWarpsM, int kWarpsN, int kStages, bool kShared>
 __global__ void __launch_bounds__(kThreads)
 attention_mma_kernel(const AttentionArgs args) {
   static_assert(kWarpsM * kWarpsN == 4, "four warps");
@@ -122,7 +124,7 @@ attention_mma_kernel(const AttentionArgs args) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_smem = reinterpret_cast<bf16*>(smem_raw);                    // [kTileM][kStride]
   bf16* k_smem = q_smem + kTileM * kStride;                            // [kStages][64][kStride]
-  bf16* v_smem = k_smem + kStages * kBlockN * kStride;                 // [kStages][64][kStride]
+  bf16* v_smem = kShared ? k_smem : k_smem + kStages * kBlockN * kStride;   // [kStages][64][kStride], or the keys' own
 
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -237,7 +239,7 @@ attention_mma_kernel(const AttentionArgs args) {
         valid = page >= 0;
         const bf16* src = valid ? head_base + page * page_stride + block_offset + copy_src[i] : args.cache;
         cp_async16(smem_u32(ks + copy_dst[i]), src, valid);
-        cp_async16(smem_u32(vs + copy_dst[i]), valid ? src + v_plane : src, valid);
+        if constexpr (!kShared) cp_async16(smem_u32(vs + copy_dst[i]), valid ? src + v_plane : src, valid);
       }
       return;
     }
@@ -265,7 +267,7 @@ attention_mma_kernel(const AttentionArgs args) {
         }
       }
       cp_async16(smem_u32(ks + r * kStride + c * 8), src, valid);
-      cp_async16(smem_u32(vs + r * kStride + c * 8), valid ? src + v_plane : src, valid);
+      if constexpr (!kShared) cp_async16(smem_u32(vs + r * kStride + c * 8), valid ? src + v_plane : src, valid);
     }
   };
 
@@ -443,7 +445,7 @@ attention_mma_kernel(const AttentionArgs args) {
     constexpr int kMergeStride = kD + 4;
     float* merge_o = reinterpret_cast<float*>(k_smem);                 // [kWarpsN][16][kMergeStride]
     float* merge_ml = merge_o + kWarpsN * 16 * kMergeStride;           // [kWarpsN][16][2]
-    static_assert((kWarpsN * 16 * (kMergeStride + 2)) * 4 <= 2 * kStages * kBlockN * kStride * 2,
+    static_assert((kWarpsN * 16 * (kMergeStride + 2)) * 4 <= (kShared ? 1 : 2) * kStages * kBlockN * kStride * 2,
                   "merge buffers fit in the key/value stages");
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -523,19 +525,17 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_out,
   }
 }
 
-template <int kWarpsM, int kWarpsN, int kStages>
+template <int kWarpsM, int kWarpsN, int kStages, bool kShared>
 constexpr size_t attention_smem_bytes() {
-  return static_cast<size_t>(16 * kWarpsM + 2 * kStages * kBlockN) * kStride * sizeof(bf16);
+  return static_cast<size_t>(16 * kWarpsM + (kShared ? 1 : 2) * kStages * kBlockN) * kStride * sizeof(bf16);
 }
 
-static bool g_configured[2] = {false, false};   // [chunk tiles, decode tiles]; file-local on purpose
-
-template <int kWarpsM, int kWarpsN, int kStages>
-int launch_attention(const AttentionArgs& args, int n_items, bool pdl, cudaStream_t stream) {
-  auto kernel = attention_mma_kernel<kWarpsM, kWarpsN, kStages>;
-  constexpr size_t smem = attention_smem_bytes<kWarpsM, kWarpsN, kStages>();
+template <int kWarpsM, int kWarpsN, int kStages, bool kShared>
+int launch_attention_as(const AttentionArgs& args, int n_items, bool pdl, cudaStream_t stream) {
+  auto kernel = attention_mma_kernel<kWarpsM, kWarpsN, kStages, kShared>;
+  constexpr size_t smem = attention_smem_bytes<kWarpsM, kWarpsN, kStages, kShared>();
   static_assert(smem <= 227 * 1024, "shared memory of one CTA");
-  bool& configured = g_configured[kWarpsN == 1 ? 0 : 1];
+  static bool configured = false;   // one per instantiation and per library image
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
@@ -543,6 +543,12 @@ int launch_attention(const AttentionArgs& args, int n_items, bool pdl, cudaStrea
     configured = true;
   }
   return launch_kernel(kernel, dim3(args.hkv, n_items), dim3(kThreads), smem, stream, pdl, args);
+}
+
+template <int kWarpsM, int kWarpsN, int kStages>
+int launch_attention(const AttentionArgs& args, int n_items, bool pdl, cudaStream_t stream) {
+  return args.kv_planes == 1 ? launch_attention_as<kWarpsM, kWarpsN, kStages, true>(args, n_items, pdl, stream)
+                             : launch_attention_as<kWarpsM, kWarpsN, kStages, false>(args, n_items, pdl, stream);
 }
 
 }  // namespace RL_ATTENTION_NS

@@ -180,6 +180,45 @@ __global__ void __launch_bounds__(256) heads_linear_kernel(const T* __restrict__
   }
 }
 
+// The same product for a step of few tokens, where a 64 x 64 tile would be mostly empty rows and the heads x
+// columns / 64 CTAs too few: a warp per output column.  The warp keeps its weight row in registers (lane l holds
+// k = l, l + 32, ..., so K <= 32 * kHeadRowRegs), and for every token multiplies it with the token's row (read
+// through L1 by the eight warps of a CTA) and adds the lanes' sums down a fixed tree.
+// A CTA takes kHeadTokensPerCta tokens, so a step of 64 tokens is eight times the CTAs and not eight times the walk.
+// bfloat16 only: float32 keeps the tiles at every size, so that its sums have one order however a prompt is cut.
+constexpr int kHeadRowRegs = 8, kHeadColumnsPerCta = 8, kHeadTokensPerCta = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kHeadColumnsPerCta) heads_linear_few_kernel(
+    const T* __restrict__ x, int x_width, int x_col0, const T* __restrict__ w, T* __restrict__ out, int out_width,
+    int tokens, int heads, int N, int K) {
+  pdl_trigger();
+  const int h = blockIdx.x, lane = threadIdx.x & 31;
+  const int n = blockIdx.y * kHeadColumnsPerCta + (threadIdx.x >> 5);
+  if (n >= N) return;
+  const T* row = w + (static_cast<size_t>(h) * N + n) * K;
+  float wr[kHeadRowRegs];
+#pragma unroll
+  for (int i = 0; i < kHeadRowRegs; ++i) {
+    const int k = lane + 32 * i;
+    wr[i] = k < K ? to_float(row[k]) : 0.0f;         // weights: no kernel of the step wrote them
+  }
+  pdl_wait();
+  const int t_end = min(tokens, (static_cast<int>(blockIdx.z) + 1) * kHeadTokensPerCta);
+  for (int t = blockIdx.z * kHeadTokensPerCta; t < t_end; ++t) {
+    const T* xr = x + (static_cast<size_t>(t) * heads + h) * x_width + x_col0;
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kHeadRowRegs; ++i) {
+      const int k = lane + 32 * i;
+      if (k < K) sum = fmaf(to_float(xr[k]), wr[i], sum);
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+    if (lane == 0) out[(static_cast<size_t>(t) * heads + h) * out_width + n] = from_float<T>(sum);
+  }
+}
+
 inline unsigned flat_grid(long long total, int threads) {
   const long long blocks = (total + threads - 1) / threads;
   return static_cast<unsigned>(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
@@ -238,6 +277,16 @@ int rl_heads_linear(int dtype, const void* x, int x_width, int x_col0, const voi
   if (tokens == 0 || n_out == 0) return 0;
   if (heads < 1 || heads > 65535 || k < 1 || x_col0 < 0 || x_col0 + k > x_width || n_out > out_width)
     return static_cast<int>(cudaErrorInvalidValue);
+  if (dtype == rl::kBF16 && tokens <= rl::kHeadTile && k <= 32 * rl::kHeadRowRegs) {
+    const dim3 few(heads, (n_out + rl::kHeadColumnsPerCta - 1) / rl::kHeadColumnsPerCta,
+                   (tokens + rl::kHeadTokensPerCta - 1) / rl::kHeadTokensPerCta);
+    RL_DISPATCH_DTYPE(dtype, {
+      return rl::launch_kernel(rl::heads_linear_few_kernel<scalar_t>, few, dim3(32 * rl::kHeadColumnsPerCta), 0, stream,
+                               pdl != 0, static_cast<const scalar_t*>(x), x_width, x_col0, static_cast<const scalar_t*>(w),
+                               static_cast<scalar_t*>(out), out_width, tokens, heads, n_out, k);
+    });
+    return 0;
+  }
   const dim3 grid((tokens + rl::kHeadTile - 1) / rl::kHeadTile, (n_out + rl::kHeadTile - 1) / rl::kHeadTile, heads);
   RL_DISPATCH_DTYPE(dtype, {
     return rl::launch_kernel(rl::heads_linear_kernel<scalar_t>, grid, dim3(256), 0, stream, pdl != 0,

@@ -55,7 +55,7 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
 
     from ..parts.attention import AttentionItems
     from ..parts.base import StepShape
-    from . import kernels
+    from . import gemm, kernels
 
     device = "cuda:0"
     heads, d, q_rank = width // 128, 256, 3 * width // 8
@@ -111,7 +111,7 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
         uk_t, uv = bf(heads, KV_RANK, PLAIN), bf(heads, VDIM, KV_RANK)
         timed("heads_linear, queries into the latent", tokens, entries,
               tokens * heads * (PLAIN + KV_RANK) * 2 + uk_t.numel() * 2,
-              lambda: kernels.heads_linear(q, uk_t, wide), flops=2.0 * tokens * heads * PLAIN * KV_RANK)
+              lambda: gemm.heads_linear(q, uk_t, wide), flops=2.0 * tokens * heads * PLAIN * KV_RANK)
         timed("latent_rotate_queries", tokens, entries, tokens * heads * (ROT + d - KV_RANK) * 2,
               lambda: kernels.latent_rotate_queries(q, wide, heads=heads, dim=PLAIN, rot=ROT, kv_rank=KV_RANK, positions=positions,
                                                     freq=freq, magnitude=1.2, layout=kernels.ROTATE_NEIGHBOURS))
@@ -138,7 +138,7 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
         values = torch.empty(tokens, heads * VDIM, dtype=torch.bfloat16, device=device)
         timed("heads_linear, values out of the latent", tokens, entries,
               tokens * heads * (KV_RANK + VDIM) * 2 + uv.numel() * 2,
-              lambda: kernels.heads_linear(attended, uv, values), flops=2.0 * tokens * heads * VDIM * KV_RANK)
+              lambda: gemm.heads_linear(attended, uv, values), flops=2.0 * tokens * heads * VDIM * KV_RANK)
         timed("sigmoid_scale_heads", tokens, entries, tokens * heads * VDIM * 4,
               lambda: kernels.sigmoid_scale_heads(values, down[:, c_col0 + d :], heads=heads))
         # -- the recurrent mixer: blends, decay, the walk with a bonus, norm and gate

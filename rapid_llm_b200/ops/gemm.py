@@ -177,6 +177,31 @@ def linear(x, weight: torch.Tensor, out: torch.Tensor, fault: torch.Tensor | Non
     return out
 
 
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, x_col0: int = 0) -> torch.Tensor:
+    """A product per head, ``out[t, h, :N] = x[t, h, x_col0 : x_col0 + K] @ weight[h]^T`` with ``weight [heads, N, K]``,
+    ``x [T, heads * x_width]`` and ``out [T, heads * out_width]``; columns of ``out`` behind ``N`` in a head stay.
+
+    float32 and bfloat16 steps of up to :data:`TENSOR_CORE_MAX_TOKENS` tokens run the hand-written tiles
+    (:func:`kernels.heads_linear`: true 32-bit sums in a fixed order); larger bfloat16 steps call the library's
+    batched product over strided views of ``x`` and ``out`` (nothing is copied: a head's rows lie ``heads * width``
+    apart), as :func:`linear` calls the library at those sizes."""
+    if x.dtype != torch.bfloat16 or x.shape[0] <= TENSOR_CORE_MAX_TOKENS or FORCE == "tcgen05":
+        return kernels.heads_linear(x, weight, out, x_col0=x_col0)
+    heads, n_out, k = weight.shape
+    tokens = x.shape[0]
+    if (x.dtype != weight.dtype or out.dtype != x.dtype or x.shape[1] % heads or out.shape[1] % heads
+            or out.shape[0] != tokens or not (x.is_contiguous() and out.is_contiguous() and weight.is_contiguous())):
+        raise kernels.KernelError("heads_linear: shapes or dtypes do not agree")
+    x_width, out_width = x.shape[1] // heads, out.shape[1] // heads
+    if x_col0 < 0 or x_col0 + k > x_width or n_out > out_width:
+        raise kernels.KernelError("heads_linear: a head's columns lie outside its rows")
+    flush()
+    rows = x.view(tokens, heads, x_width)[:, :, x_col0 : x_col0 + k].transpose(0, 1)           # [heads, T, K]
+    into = out.view(tokens, heads, out_width)[:, :, :n_out].transpose(0, 1)                    # [heads, T, N]
+    torch.bmm(rows, weight.transpose(1, 2), out=into)
+    return out
+
+
 def gated_linear(x, gate_up: torch.Tensor, act: torch.Tensor, workspace, fault: torch.Tensor, *,
                  defer: bool = False, clamp: tuple[float, float] | None = None) -> torch.Tensor:
     """``act = silu(x @ gate^T) * (x @ up^T)`` for a ``[2 I, K]`` weight with the gate rows first; with

@@ -10,7 +10,7 @@ numbers per token (``CacheNeed.token_shape``).
 
 Nothing is expanded per key.  Since ``q_plain . W_uk_h c = (W_uk_h^T q_plain) . c`` and
 ``sum_j p_j W_uv_h c_j = W_uv_h sum_j p_j c_j``, a step moves ``W_uk`` to the queries (a product per head,
-``ops.kernels.heads_linear``) and ``W_uv`` behind the attention, and the attention in between is the paged kernels'
+``ops.gemm.heads_linear``) and ``W_uv`` behind the attention, and the attention in between is the paged kernels'
 case of ONE key/value head of width ``D`` shared by all query heads, whose values are the keys' own rows (a cache of
 one plane).  The zero-padded columns and the ``k_r`` columns of the attended rows meet no column of ``W_uv``.
 
@@ -159,14 +159,14 @@ class LatentAttention(Mixer):
         q = gemm.linear(c_q, self.uq, space.get("latent_q", rows, self.uq.shape[0], x.dtype), batch.fault)
         gemm.flush()
         wide = space.get("latent_wide", rows, self.h * self.d, x.dtype)
-        kernels.heads_linear(q, self.uk_t, wide)                  # columns [0, kv_rank) of every head
+        gemm.heads_linear(q, self.uk_t, wide)                  # columns [0, kv_rank) of every head
         kernels.latent_rotate_queries(q, wide, heads=self.h, dim=self.dim, rot=self.rot, kv_rank=self.kv_rank,
                                       positions=batch.positions, freq=self.freq, magnitude=self.magnitude,
                                       layout=self.layout)
         attended = space.get("latent_attended", rows, self.h * self.d, x.dtype)
         self._attend(wide, pages.view(pages.shape[0], 1, 1, pages.shape[1], self.d), attended, batch, group)
         values = space.get("latent_values", rows, self.h * self.vdim, x.dtype)
-        kernels.heads_linear(attended, self.uv, values)
+        gemm.heads_linear(attended, self.uv, values)
         if self.has_gate:
             kernels.sigmoid_scale_heads(values, down[:, self.g_col0 :], heads=self.h)
         return gemm.linear(values, self.o, space.get("latent_out", rows, self.hidden, x.dtype), batch.fault)

@@ -99,15 +99,18 @@ def test_latent_rotate_queries(heads, dim, rot, kv_rank, width, neighbours, dtyp
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("tokens,heads,n_out,k,x_width,out_width,x_col0", [
     (33, 3, 40, 16, 24, 48, 0), (1, 5, 14, 10, 16, 32, 0), (200, 16, 192, 24, 88, 256, 0), (17, 2, 24, 32, 48, 24, 0),
-    (9, 4, 6, 22, 32, 6, 2), (70, 1, 64, 96, 96, 64, 0)])
-def test_a_product_per_head(tokens, heads, n_out, k, x_width, out_width, x_col0, dtype):
-    from rapid_llm_b200.ops import kernels
+    (9, 4, 6, 22, 32, 6, 2), (70, 1, 64, 96, 96, 64, 0), (90, 3, 10, 14, 18, 13, 1), (2048, 8, 192, 128, 192, 256, 0)])
+@pytest.mark.parametrize("entry", ["tiles", "by size"])
+def test_a_product_per_head(tokens, heads, n_out, k, x_width, out_width, x_col0, dtype, entry):
+    """The hand-written tiles at every size, and the entry point that hands large bfloat16 steps to the library's
+    batched product over strided views (rows that start at odd columns too)."""
+    from rapid_llm_b200.ops import gemm, kernels
 
     g = torch.Generator().manual_seed(tokens + heads)
     x = torch.randn(tokens, heads * x_width, generator=g).to(dtype).to(DEVICE)
     weight = (torch.randn(heads, n_out, k, generator=g) / math.sqrt(k)).to(dtype).to(DEVICE)
     out = torch.full((tokens, heads * out_width), 5.0, dtype=dtype, device=DEVICE)
-    kernels.heads_linear(x, weight, out, x_col0=x_col0)
+    (kernels if entry == "tiles" else gemm).heads_linear(x, weight, out, x_col0=x_col0)
     got = out.view(tokens, heads, out_width).float()
     want = torch.einsum("thk,hnk->thn", x.view(tokens, heads, x_width)[..., x_col0 : x_col0 + k].double(), weight.double()).float()
     torch.testing.assert_close(got[..., :n_out], want.to(dtype).float(), **_tolerance(dtype))
