@@ -107,11 +107,28 @@ __global__ void latent_rotate_queries_kernel(const T* __restrict__ q, int heads,
 
 // ------------------------------------------------------------ one number per head as a sigmoid gate
 // rows[t, h, 0:width] *= sigmoid(gate[t, gate_col0 + h]), in place.
-template <typename T>
+// kVec elements (16 bytes) a thread and round where a head's width is a multiple of kVec; else one.
+template <typename T, int kVec>
 __global__ void sigmoid_scale_heads_kernel(T* __restrict__ rows, int heads, int width, const T* __restrict__ gate,
                                            int gate_stride, int gate_col0, long long total) {
   pdl_trigger();
   pdl_wait();
+  if constexpr (kVec > 1) {
+    const int per_head = width / kVec;
+    for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total / kVec;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long head_at = idx / per_head;
+      const long long t = head_at / heads;
+      const int h = static_cast<int>(head_at - t * heads);
+      const float g = sigmoid_exact(to_float(gate[static_cast<size_t>(t) * gate_stride + gate_col0 + h]));
+      uint4 raw = reinterpret_cast<const uint4*>(rows)[idx];
+      T* part = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) part[i] = from_float<T>(to_float(part[i]) * g);
+      reinterpret_cast<uint4*>(rows)[idx] = raw;
+    }
+    return;
+  }
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long head_at = idx / width;
@@ -265,7 +282,12 @@ int rl_sigmoid_scale_heads(int dtype, void* rows, int heads, int width, const vo
   const long long total = static_cast<long long>(tokens) * heads * width;
   if (total == 0) return 0;
   RL_DISPATCH_DTYPE(dtype, {
-    return rl::launch_kernel(rl::sigmoid_scale_heads_kernel<scalar_t>, dim3(rl::flat_grid(total, 256)), dim3(256), 0,
+    constexpr int kVec = 16 / static_cast<int>(sizeof(scalar_t));
+    if (width % kVec == 0 && reinterpret_cast<uintptr_t>(rows) % 16 == 0)
+      return rl::launch_kernel(rl::sigmoid_scale_heads_kernel<scalar_t, kVec>, dim3(rl::flat_grid(total / kVec, 256)),
+                               dim3(256), 0, stream, pdl != 0, static_cast<scalar_t*>(rows), heads, width,
+                               static_cast<const scalar_t*>(gate), gate_stride, gate_col0, total);
+    return rl::launch_kernel(rl::sigmoid_scale_heads_kernel<scalar_t, 1>, dim3(rl::flat_grid(total, 256)), dim3(256), 0,
                              stream, pdl != 0, static_cast<scalar_t*>(rows), heads, width,
                              static_cast<const scalar_t*>(gate), gate_stride, gate_col0, total);
   });
