@@ -6,6 +6,7 @@ from .basitar import BasitarConfig
 from .kopatar import KopatarConfig
 from .mezadra import MezadraConfig
 from .qwen3 import Qwen3Config
+from .zupupel import ZupupelConfig
 from .registry import (
     load_config,
     read_config_json,
@@ -18,6 +19,7 @@ register_architecture(Qwen3Config)
 register_architecture(KopatarConfig)
 register_architecture(MezadraConfig)
 register_architecture(BasitarConfig)
+register_architecture(ZupupelConfig)
 
 __all__ = [
     "BasitarConfig",
@@ -29,6 +31,7 @@ __all__ = [
     "PartSpec",
     "Qwen3Config",
     "ScheduleEntry",
+    "ZupupelConfig",
     "load_config",
     "parse_dtype",
     "read_config_json",

@@ -56,6 +56,7 @@ class LayerSpec:
     norm: PartSpec
     prefix: str
     names: Mapping[str, str] | None = None   # checkpoint sub-prefixes of the layer's parts, where they differ from the arrangement's
+    arrangement_params: Mapping[str, Any] | None = None   # constants of the arrangement itself (a weight on the stream, ...)
 
 
 @dataclass(frozen=True)

@@ -253,6 +253,94 @@ __global__ void add_rmsnorm_kernel(const TX* __restrict__ x, float* __restrict__
   }
 }
 
+// ------------------------------------------------------------ layer norm (mean, variance, weight, bias)
+// One block per output row; row i reads input row `row_index[i]` (or i).  With r = x + res_scale * residual
+// (either operand may be absent), the norm is n = (r - mean(r)) * rsqrt(var(r) + eps) * weight + bias, the
+// variance being the mean of the squared deviations (formed in a second pass over the row's values, which stay
+// in registers or shared memory), all float32.  `store` 1 puts the sum r back into `residual` (a norm in front
+// of a sublayer), 2 puts the norm n there (a norm behind the sum: the stream's new value is the norm itself).
+// out = n * gain, rounded once to the engine's dtype.
+template <typename T, bool kVector>
+__global__ void layernorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
+                                 const float* __restrict__ weight, const float* __restrict__ bias,
+                                 T* __restrict__ out, const int* __restrict__ row_index, int hidden, float eps,
+                                 float res_scale, int store, float gain) {
+  extern __shared__ float row_values[];  // [hidden] on the element-by-element path
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int out_row = blockIdx.x;
+  const int in_row = row_index ? row_index[out_row] : out_row;
+  const T* xr = x ? x + static_cast<size_t>(in_row) * hidden : nullptr;
+  float* rr = residual ? residual + static_cast<size_t>(in_row) * hidden : nullptr;
+  T* o = out + static_cast<size_t>(out_row) * hidden;
+  const float count = static_cast<float>(hidden);
+  if constexpr (kVector) {
+    const int at = threadIdx.x * 8;
+    const bool active = at < hidden;
+    float w[8], b[8], v[8];
+    if (active) {
+      load8(weight + at, w);
+      if (bias) load8(bias + at, b);
+    }
+    pdl_wait();
+    float sum = 0.0f;
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+      if (xr) load8(xr + at, v);
+      if (rr) {
+        float r[8];
+        load8(rr + at, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = fmaf(res_scale, r[i], v[i]);
+      }
+      if (store == 1) store8(rr + at, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += v[i];
+    }
+    const float mean = block_sum(sum, scratch) / count;
+    float dev = 0.0f;
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] -= mean;
+        dev += v[i] * v[i];
+      }
+    }
+    const float inv = rsqrtf(block_sum(dev, scratch) / count + eps);
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * w[i] + (bias ? b[i] : 0.0f);
+      if (store == 2) store8(rr + at, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] *= gain;
+      store8(o + at, v);
+    }
+  } else {
+    pdl_wait();
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = xr ? to_float(xr[i]) : 0.0f;
+      if (rr) v = fmaf(res_scale, rr[i], v);
+      if (store == 1) rr[i] = v;
+      row_values[i] = v;
+      sum += v;
+    }
+    const float mean = block_sum(sum, scratch) / count;
+    float dev = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = row_values[i] - mean;
+      dev += d * d;
+    }
+    const float inv = rsqrtf(block_sum(dev, scratch) / count + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float n = (row_values[i] - mean) * inv * weight[i] + (bias ? bias[i] : 0.0f);
+      if (store == 2) rr[i] = n;
+      o[i] = from_float<T>(n * gain);
+    }
+  }
+}
+
 // ---------------------------------------------------------------- SiLU * up
 // gate_up is [rows, 2 * inter] with the gate in columns [0, inter) and up in
 // [inter, 2 * inter); out[r, c] = silu(gate) * up with silu(z) = z * sigmoid(z), in float32.
@@ -411,6 +499,39 @@ int rl_add_rmsnorm(int dtype, const void* x, float* residual, const float* weigh
                              static_cast<const scalar_t*>(x), residual, weight, static_cast<scalar_t*>(out),
                              row_index, hidden, eps, mode, write_residual,
                              static_cast<const scalar_t*>(extra_rows), extra_vector);
+  });
+  return 0;
+}
+
+// x and out are `dtype` (x may be null: the norm of the stream alone); residual, weight and bias are float32.
+int rl_layernorm(int dtype, const void* x, float* residual, const float* weight, const float* bias, void* out,
+                 const int* row_index, int rows, int hidden, float eps, float res_scale, int store, float gain,
+                 int pdl, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (store < 0 || store > 2 || (store != 0 && residual == nullptr) || (x == nullptr && residual == nullptr) ||
+      hidden <= 0 || weight == nullptr || out == nullptr)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const bool vector = hidden % 8 == 0 && hidden <= 8 * 1024 && rl::aligned16(x) && rl::aligned16(out) &&
+                      rl::aligned16(weight) && rl::aligned16(bias) && (residual == nullptr || rl::aligned16(residual));
+  RL_DISPATCH_DTYPE(dtype, {
+    if (vector) {
+      const int threads = (hidden / 8 + 31) / 32 * 32;
+      return rl::launch_kernel(rl::layernorm_kernel<scalar_t, true>, dim3(rows), dim3(threads), 0, stream, pdl != 0,
+                               static_cast<const scalar_t*>(x), residual, weight, bias, static_cast<scalar_t*>(out),
+                               row_index, hidden, eps, res_scale, store, gain);
+    }
+    const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+    if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
+    int threads = 128;
+    while (threads < 1024 && threads * 8 < hidden) threads *= 2;
+    auto kernel = rl::layernorm_kernel<scalar_t, false>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    return rl::launch_kernel(kernel, dim3(rows), dim3(threads), smem, stream, pdl != 0,
+                             static_cast<const scalar_t*>(x), residual, weight, bias, static_cast<scalar_t*>(out),
+                             row_index, hidden, eps, res_scale, store, gain);
   });
   return 0;
 }

@@ -22,7 +22,8 @@ __device__ __forceinline__ void pair_places(int i, int rot, int layout, int& lo,
 
 // ------------------------------------------------------------ norms of the two latents, the cache row
 // One block per token.  `down` holds [query latent (q_rank) | ... | c (kv_rank) | key part (rot)] at the given
-// columns.  q_out = RMS norm of the query latent with weight wq; the cache row at kv_dest[t] receives
+// columns (q_rank 0: there is no query latent, and q_out is not touched).  q_out = RMS norm of the query latent with
+// weight wq; the cache row at kv_dest[t] receives
 // [RMS norm of c with weight wc | rotated key part | zeros up to D].
 template <typename T>
 __global__ void latent_norm_write_kernel(const T* __restrict__ down, int down_stride, int q_col0, int q_rank,
@@ -47,7 +48,7 @@ __global__ void latent_norm_write_kernel(const T* __restrict__ down, int down_st
   }
   sum_q = block_sum(sum_q, scratch);
   sum_c = block_sum(sum_c, scratch);
-  const float inv_q = rsqrtf(sum_q / static_cast<float>(q_rank) + eps);
+  const float inv_q = rsqrtf(sum_q / static_cast<float>(max(q_rank, 1)) + eps);
   const float inv_c = rsqrtf(sum_c / static_cast<float>(kv_rank) + eps);
   T* qo = q_out + static_cast<size_t>(t) * q_rank;
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x) qo[i] = from_float<T>(to_float(row[q_col0 + i]) * inv_q * wq[i]);
@@ -250,7 +251,7 @@ int rl_latent_norm_write(int dtype, const void* down, int down_stride, int q_col
                          const int* kv_dest, long long cache_rows, int D, const int* positions, const float* freq,
                          float magnitude, int layout, int tokens, int* fault, int pdl, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  if (q_rank < 1 || kv_rank < 1 || rot < 0 || rot % 2 || kv_rank + rot > D || layout < 0 || layout > 1 ||
+  if (q_rank < 0 || kv_rank < 1 || rot < 0 || rot % 2 || kv_rank + rot > D || layout < 0 || layout > 1 ||
       (rot > 0 && freq == nullptr))
     return static_cast<int>(cudaErrorInvalidValue);
   RL_DISPATCH_DTYPE(dtype, {

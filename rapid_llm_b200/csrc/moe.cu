@@ -5,13 +5,19 @@
 //   rl_router_topk    z = W_r h in float32 (W_r float32, h the engine's dtype), s = sigmoid(z), the
 //                     `top` largest per token, chosen on z (sigmoid keeps the order; ties: the lower
 //                     index) with their s as weights; extra rows of W_r behind the experts' give
-//                     sigmoid gates per token (a shared expert's).
+//                     sigmoid gates per token (a shared expert's).  Another weighting (`weigh` 2): s = softmax(z)
+//                     over all router rows; the choice is made on s + correction, among the rows of the `keep`
+//                     best of `groups` equal groups of neighbours (a group ranks by its largest corrected
+//                     score); the weights are the chosen rows' s over their sum.  Router rows behind the experts
+//                     that have tensors are identity experts: rl_moe_plan leaves their pairs out of every tile
+//                     and rl_moe_combine adds weight * the token's own row for them.
 //   rl_moe_plan       counts the pairs per expert and lays them out expert by expert in tiles of
 //                     kTileM rows: sorted[p] = i, tile tables, all on the device (no host round trip).
 //   rl_grouped_linear out rows = A rows @ W[e]^T over the tiles; A rows are fetched by token
 //                     (pair i reads row i / top) or by place p; with `gated`, W[e] is [2 F, K] (gate
 //                     rows, then up rows) and out = silu(w g) * (w u), w the pair's weight: the weight
-//                     scales the expert's input, and W (w h) = w (W h).
+//                     scales the expert's input, and W (w h) = w (W h).  With glu_limit > 0 the unit is the
+//                     clamped one: g' = min(g, limit), u' = clamp(u, +-limit), out = g' sigmoid(alpha g') (u' + 1).
 //   rl_moe_combine    out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t]), j in order, float32 sums.
 // A row's result does not depend on its tile's other rows or on the order in which the pairs of an
 // expert were laid out: the inner sums run over k in a fixed order per row.
@@ -33,6 +39,17 @@ constexpr int kMoeWideK = 64;
 constexpr int kMoeStages = 3;
 
 __device__ __forceinline__ float moe_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// The gated unit of an expert from its two float32 products: SiLU(g) * u, or with limit > 0 the clamped unit
+// min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1).
+__device__ __forceinline__ float moe_unit(float g, float u, float limit, float alpha) {
+  if (limit > 0.0f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
 
 // ------------------------------------------------------------------ router
 // One block per kRouterTokens tokens.  The block's warps share the inner range: warp w forms, for every router row
@@ -60,7 +77,8 @@ __global__ void __launch_bounds__(kRouterWarps * 32)
 router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hidden, int experts,
                    int gates, int top, int* __restrict__ ids, float* __restrict__ weights,
                    float* __restrict__ gate_out, float* __restrict__ scores_out, int tokens, int wide,
-                   const float* __restrict__ bias, int weigh) {
+                   const float* __restrict__ bias, int weigh, const float* __restrict__ correction, int groups,
+                   int keep) {
   extern __shared__ float moe_scores[];      // [kRouterTokens][rows] logits, then [kRouterWarps][kRouterTokens][rows] parts
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,11 +163,64 @@ router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hi
     for (int e = lane; e < experts; e += 32) scores_out[static_cast<size_t>(t) * experts + e] = moe_sigmoid(s[e]);
   for (int g = lane; g < gates; g += 32) gate_out[static_cast<size_t>(t) * gates + g] = moe_sigmoid(s[experts + g]);
   __syncwarp();
+  // what the choice is made on: the logits, or (weigh 2) the softmax over all rows plus a correction per row,
+  // with the rows outside the `keep` best groups at minus infinity.  The parts' memory is free by now.
+  float* pick = s;
+  if (weigh == 2) {
+    float* choice = parts + warp * rows;
+    float* group_best = parts + (kRouterTokens + warp) * rows;
+    float* group_kept = parts + (2 * kRouterTokens + warp) * rows;
+    float largest = -INFINITY;
+    for (int e = lane; e < experts; e += 32) largest = fmaxf(largest, s[e]);
+    largest = warp_max(largest);
+    float total = 0.0f;
+    for (int e = lane; e < experts; e += 32) total += expf(s[e] - largest);
+    total = warp_sum(total);
+    __syncwarp();
+    for (int e = lane; e < experts; e += 32) {
+      const float p = expf(s[e] - largest) / total;
+      s[e] = p;                                            // the plain score: what the weights are made of
+      choice[e] = p + (correction ? correction[e] : 0.0f);
+    }
+    __syncwarp();
+    if (groups > 1) {
+      const int per = experts / groups;
+      for (int g = lane; g < groups; g += 32) {
+        float m = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, choice[e]);
+        group_best[g] = m;
+        group_kept[g] = 0.0f;
+      }
+      __syncwarp();
+      for (int r = 0; r < keep; ++r) {
+        float best = -INFINITY;
+        int best_g = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32) {
+          if (group_kept[g] == 0.0f && (group_best[g] > best || best_g == 0x7fffffff)) { best = group_best[g]; best_g = g; }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+          const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+          const int other_g = __shfl_xor_sync(0xffffffffu, best_g, offset);
+          if (other_g != 0x7fffffff && (best_g == 0x7fffffff || other > best || (other == best && other_g < best_g))) {
+            best = other;
+            best_g = other_g;
+          }
+        }
+        if (lane == 0 && best_g != 0x7fffffff) group_kept[best_g] = 1.0f;
+        __syncwarp();
+      }
+      for (int e = lane; e < experts; e += 32)
+        if (group_kept[e / per] == 0.0f) choice[e] = -INFINITY;
+      __syncwarp();
+    }
+    pick = choice;
+  }
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
     for (int e = lane; e < experts; e += 32) {
-      const float v = s[e];
+      const float v = pick[e];
       if (v > best) { best = v; best_e = e; }      // a lane's lowest index wins its ties
     }
 #pragma unroll
@@ -161,8 +232,8 @@ router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hi
     if (best_e == 0x7fffffff) best_e = 0;      // every logit left is not a number: keep the index inside the table
     if (lane == 0) {
       ids[static_cast<size_t>(t) * top + j] = best_e;
-      weights[static_cast<size_t>(t) * top + j] = weigh == 1 ? best : moe_sigmoid(best);
-      s[best_e] = -INFINITY;      // taken
+      weights[static_cast<size_t>(t) * top + j] = weigh == 2 ? s[best_e] : (weigh == 1 ? best : moe_sigmoid(best));
+      pick[best_e] = -INFINITY;      // taken
     }
     __syncwarp();
   }
@@ -175,6 +246,14 @@ router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hi
       w[j] = expf(w[j] - largest);
       sum += w[j];
     }
+    for (int j = 0; j < top; ++j) w[j] = w[j] / sum;
+  }
+  if (weigh == 2 && lane == 0) {
+    // the chosen rows' scores over their sum, added up in the order of the choices
+    float* w = weights + static_cast<size_t>(t) * top;
+    float sum = 0.0f;
+    for (int j = 0; j < top; ++j) sum += w[j];
+    sum += 1e-20f;
     for (int j = 0; j < top; ++j) w[j] = w[j] / sum;
   }
 }
@@ -235,7 +314,7 @@ template <typename T, bool kGated>
 __global__ void __launch_bounds__(kMoeThreads)
 grouped_linear_fma_kernel(const T* a, int a_stride, const T* __restrict__ w, const int* __restrict__ sorted,
                           const int* __restrict__ meta, const float* __restrict__ pair_weight, int top, int by_token,
-                          int n, int k, T* out_act, float* out_y) {
+                          int n, int k, T* out_act, float* out_y, float glu_limit, float glu_alpha) {
   __shared__ float sa[kMoeTileM][kMoeTileK + 1];
   __shared__ float sw[kGated ? 2 : 1][kMoeTileN][kMoeTileK + 1];
   __shared__ int s_pair[kMoeTileM];
@@ -303,7 +382,7 @@ grouped_linear_fma_kernel(const T* a, int a_stride, const T* __restrict__ w, con
       if constexpr (kGated) {
         const float scale = pair_weight ? pair_weight[pair] : 1.0f;
         const float g = acc[0][r][c] * scale, u = acc[1][r][c] * scale;
-        out_act[static_cast<size_t>(place0 + row) * n + col] = from_float<T>(g / (1.0f + expf(-g)) * u);
+        out_act[static_cast<size_t>(place0 + row) * n + col] = from_float<T>(moe_unit(g, u, glu_limit, glu_alpha));
       } else {
         out_y[static_cast<size_t>(pair) * n + col] = acc[0][r][c];
       }
@@ -327,7 +406,7 @@ __global__ void __launch_bounds__(kMoeThreads)
 grouped_linear_mma_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bfloat16* __restrict__ w,
                           const int* __restrict__ sorted, const int* __restrict__ meta,
                           const float* __restrict__ pair_weight, int top, int by_token, int n, int k,
-                          __nv_bfloat16* out_act, float* out_y) {
+                          __nv_bfloat16* out_act, float* out_y, float glu_limit, float glu_alpha) {
   constexpr int kStride = kMoeTileK + 8;      // elements; rows stay 16-byte aligned and spread over the banks
   __shared__ __align__(16) __nv_bfloat16 sa[kMoeTileM][kStride];
   __shared__ __align__(16) __nv_bfloat16 sw[kGated ? 2 : 1][kMoeTileN][kStride];
@@ -436,7 +515,7 @@ grouped_linear_mma_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bfloa
         if (col >= n) continue;
         if constexpr (kGated) {
           const float g = acc[0][t][2 * half + c] * scale, u = acc[1][t][2 * half + c] * scale;
-          out_act[static_cast<size_t>(place0 + row) * n + col] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+          out_act[static_cast<size_t>(place0 + row) * n + col] = __float2bfloat16_rn(moe_unit(g, u, glu_limit, glu_alpha));
         } else {
           out_y[static_cast<size_t>(pair) * n + col] = acc[0][t][2 * half + c];
         }
@@ -471,7 +550,7 @@ __global__ void __launch_bounds__(kMoeThreads)
 grouped_linear_wide_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bfloat16* __restrict__ w,
                            const int* __restrict__ sorted, const int* __restrict__ meta,
                            const float* __restrict__ pair_weight, int top, int by_token, int n, int k,
-                           __nv_bfloat16* out_act, float* out_y) {
+                           __nv_bfloat16* out_act, float* out_y, float glu_limit, float glu_alpha) {
   constexpr int kStride = kMoeWideK + 8;
   constexpr int kWRows = (kGated ? 2 : 1) * kMoeTileN;
   constexpr int kStageElems = (kMoeWideM + kWRows) * kStride;
@@ -590,7 +669,7 @@ grouped_linear_wide_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bflo
           if (col >= n) continue;
           if constexpr (kGated) {
             const float g = acc[0][mt][nt][2 * half + c] * scale, u = acc[1][mt][nt][2 * half + c] * scale;
-            out_act[static_cast<size_t>(place0 + row) * n + col] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+            out_act[static_cast<size_t>(place0 + row) * n + col] = __float2bfloat16_rn(moe_unit(g, u, glu_limit, glu_alpha));
           } else {
             out_y[static_cast<size_t>(pair) * n + col] = acc[0][mt][nt][2 * half + c];
           }
@@ -603,7 +682,8 @@ grouped_linear_wide_kernel(const __nv_bfloat16* a, int a_stride, const __nv_bflo
 // ------------------------------------------------------------------ combine
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T* shared, const float* __restrict__ gate,
-                                   int gate_stride, T* __restrict__ out, int tokens, int hidden, const float* weights) {
+                                   int gate_stride, T* __restrict__ out, int tokens, int hidden, const float* weights,
+                                   const int* __restrict__ ids, int experts, const T* __restrict__ x, int x_stride) {
   pdl_trigger();
   pdl_wait();
   const long long total = static_cast<long long>(tokens) * hidden;
@@ -612,7 +692,14 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T
     const long long t = idx / hidden;
     const int c = static_cast<int>(idx - t * hidden);
     float sum = 0.0f;
-    if (weights) {
+    if (ids) {
+      // a choice at or behind `experts` is an identity expert: its result is the token's own row, and no tile wrote y
+      const float own = to_float(x[t * x_stride + c]);
+      for (int j = 0; j < top; ++j) {
+        const float v = ids[t * top + j] >= experts ? own : y[(t * top + j) * hidden + c];
+        sum = weights ? fmaf(weights[t * top + j], v, sum) : sum + v;
+      }
+    } else if (weights) {
       for (int j = 0; j < top; ++j) sum = fmaf(weights[t * top + j], y[(t * top + j) * hidden + c], sum);
     } else {
       for (int j = 0; j < top; ++j) sum += y[(t * top + j) * hidden + c];
@@ -630,12 +717,16 @@ int rl_moe_tile_rows(int wide) { return wide ? rl::kMoeWideM : rl::kMoeTileM; }
 
 int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int hidden, int experts, int gates, int top,
                    int* ids, float* weights, float* gate_out, float* scores_out, int tokens, const float* bias,
-                   int weigh, int pdl, cudaStream_t stream) {
+                   int weigh, const float* correction, int groups, int keep, int pdl, cudaStream_t stream) {
   // bias: one float per expert added to its logit, or null.  weigh 0: a chosen expert's weight is the sigmoid of its
-  // logit; 1: the softmax over the chosen logits.
+  // logit; 1: the softmax over the chosen logits; 2: the softmax over all rows, chosen on it plus `correction` (one
+  // float per row, or null) within the `keep` best of `groups` groups, the chosen scores divided by their sum.
   if (tokens == 0) return 0;
   if (experts < 1 || top < 1 || top > experts || gates < 0 || (gates > 0 && gate_out == nullptr) || hidden < 1 ||
-      weigh < 0 || weigh > 1)
+      weigh < 0 || weigh > 2)
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (weigh == 2 && (groups < 1 || experts % groups != 0 || keep < 1 || keep > groups || bias != nullptr ||
+                     top > keep * (experts / groups)))
     return static_cast<int>(cudaErrorInvalidValue);
   const size_t smem = static_cast<size_t>(rl::kRouterTokens) * (rl::kRouterWarps + 1) * (experts + gates) * sizeof(float);
   if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
@@ -651,7 +742,8 @@ int rl_router_topk(int dtype, const void* x, int x_stride, const float* w, int h
     return rl::launch_kernel(rl::router_topk_kernel<scalar_t>,
                              dim3((tokens + rl::kRouterTokens - 1) / rl::kRouterTokens), dim3(rl::kRouterWarps * 32),
                              smem, stream, pdl != 0, static_cast<const scalar_t*>(x), x_stride, w, hidden, experts,
-                             gates, top, ids, weights, gate_out, scores_out, tokens, wide, bias, weigh);
+                             gates, top, ids, weights, gate_out, scores_out, tokens, wide, bias, weigh, correction,
+                             groups, keep);
   });
   return 0;
 }
@@ -673,7 +765,8 @@ int rl_moe_plan(const int* ids, int pairs, int experts, int* sorted, int* place_
 template <bool kGated>
 static int launch_grouped_wide(dim3 grid, cudaStream_t stream, bool pdl, const __nv_bfloat16* a, int a_stride,
                                const __nv_bfloat16* w, const int* sorted, const int* meta, const float* pair_weight,
-                               int top, int by_token, int n, int k, __nv_bfloat16* out_act, float* out_y) {
+                               int top, int by_token, int n, int k, __nv_bfloat16* out_act, float* out_y,
+                               float glu_limit, float glu_alpha) {
   static bool configured = false;
   auto kernel = rl::grouped_linear_wide_kernel<kGated>;
   constexpr int smem = rl::moe_wide_smem_bytes<kGated>();
@@ -683,7 +776,7 @@ static int launch_grouped_wide(dim3 grid, cudaStream_t stream, bool pdl, const _
     configured = true;
   }
   return rl::launch_kernel(kernel, grid, dim3(rl::kMoeThreads), smem, stream, pdl, a, a_stride, w, sorted, meta,
-                           pair_weight, top, by_token, n, k, out_act, out_y);
+                           pair_weight, top, by_token, n, k, out_act, out_y, glu_limit, glu_alpha);
 }
 
 extern "C" {
@@ -691,7 +784,8 @@ extern "C" {
 // tile_m: the rows of a tile the plan was made with; kMoeWideM selects the pipelined bfloat16 kernel.
 int rl_grouped_linear(int dtype, const void* a, int a_stride, const void* w, const int* sorted, const int* meta,
                       const float* pair_weight, int top, int by_token, int n, int k, int gated, void* out_act,
-                      float* out_y, int max_tiles, int tile_m, int pdl, cudaStream_t stream) {
+                      float* out_y, int max_tiles, int tile_m, float glu_limit, float glu_alpha, int pdl,
+                      cudaStream_t stream) {
   if (max_tiles == 0) return 0;
   if (tile_m == rl::kMoeWideM) {
     using bf = __nv_bfloat16;
@@ -702,10 +796,10 @@ int rl_grouped_linear(int dtype, const void* a, int a_stride, const void* w, con
     if (gated)
       return launch_grouped_wide<true>(wide_grid, stream, pdl != 0, static_cast<const bf*>(a), a_stride,
                                        static_cast<const bf*>(w), sorted, meta, pair_weight, top, by_token, n, k,
-                                       static_cast<bf*>(out_act), out_y);
+                                       static_cast<bf*>(out_act), out_y, glu_limit, glu_alpha);
     return launch_grouped_wide<false>(wide_grid, stream, pdl != 0, static_cast<const bf*>(a), a_stride,
                                       static_cast<const bf*>(w), sorted, meta, pair_weight, top, by_token, n, k,
-                                      static_cast<bf*>(out_act), out_y);
+                                      static_cast<bf*>(out_act), out_y, glu_limit, glu_alpha);
   }
   if (tile_m != rl::kMoeTileM) return static_cast<int>(cudaErrorInvalidValue);
   if (n < 1 || k < 1 || top < 1 || (gated && out_act == nullptr) || (!gated && out_y == nullptr) || max_tiles > 65535)
@@ -716,32 +810,36 @@ int rl_grouped_linear(int dtype, const void* a, int a_stride, const void* w, con
     if (gated)
       return rl::launch_kernel(rl::grouped_linear_mma_kernel<true>, grid, block, 0, stream, pdl != 0,
                                static_cast<const bf*>(a), a_stride, static_cast<const bf*>(w), sorted, meta, pair_weight,
-                               top, by_token, n, k, static_cast<bf*>(out_act), out_y);
+                               top, by_token, n, k, static_cast<bf*>(out_act), out_y, glu_limit, glu_alpha);
     return rl::launch_kernel(rl::grouped_linear_mma_kernel<false>, grid, block, 0, stream, pdl != 0,
                              static_cast<const bf*>(a), a_stride, static_cast<const bf*>(w), sorted, meta, pair_weight,
-                             top, by_token, n, k, static_cast<bf*>(out_act), out_y);
+                             top, by_token, n, k, static_cast<bf*>(out_act), out_y, glu_limit, glu_alpha);
   }
   if (dtype != rl::kF32) return static_cast<int>(cudaErrorInvalidValue);
   if (gated)
     return rl::launch_kernel(rl::grouped_linear_fma_kernel<float, true>, grid, block, 0, stream, pdl != 0,
                              static_cast<const float*>(a), a_stride, static_cast<const float*>(w), sorted, meta,
-                             pair_weight, top, by_token, n, k, static_cast<float*>(out_act), out_y);
+                             pair_weight, top, by_token, n, k, static_cast<float*>(out_act), out_y, glu_limit, glu_alpha);
   return rl::launch_kernel(rl::grouped_linear_fma_kernel<float, false>, grid, block, 0, stream, pdl != 0,
                            static_cast<const float*>(a), a_stride, static_cast<const float*>(w), sorted, meta,
-                           pair_weight, top, by_token, n, k, static_cast<float*>(out_act), out_y);
+                           pair_weight, top, by_token, n, k, static_cast<float*>(out_act), out_y, glu_limit, glu_alpha);
 }
 
-// weights: one float per (token, choice) that multiplies the choice's row in the sum, or null.
+// weights: one float per (token, choice) that multiplies the choice's row in the sum, or null.  ids (with x, the
+// experts' input rows): a choice whose id is `experts` or more is an identity expert and contributes x's row.
 int rl_moe_combine(int dtype, const float* y, int top, const void* shared, const float* gate, int gate_stride,
-                   void* out, int tokens, int hidden, const float* weights, int pdl, cudaStream_t stream) {
+                   void* out, int tokens, int hidden, const float* weights, const int* ids, int experts, const void* x,
+                   int x_stride, int pdl, cudaStream_t stream) {
   if (tokens == 0) return 0;
+  if (ids != nullptr && x == nullptr) return static_cast<int>(cudaErrorInvalidValue);
   const long long total = static_cast<long long>(tokens) * hidden;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   RL_DISPATCH_DTYPE(dtype, {
     return rl::launch_kernel(rl::moe_combine_kernel<scalar_t>, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream,
                              pdl != 0, y, top, static_cast<const scalar_t*>(shared), gate, gate_stride,
-                             static_cast<scalar_t*>(out), tokens, hidden, weights);
+                             static_cast<scalar_t*>(out), tokens, hidden, weights, ids, experts,
+                             static_cast<const scalar_t*>(x), x_stride);
   });
   return 0;
 }

@@ -487,7 +487,102 @@ __global__ void rope_unit_write_kernel(const RopeUnitArgs a) {
   }
 }
 
+// ------------------------------------------------------------ norm over the whole projection, rotation, cache write
+// For mixers whose q and k are normed over ALL their heads at once, before they are split: with q the token's
+// whole query row (hq * d numbers, heads laid out in d with their padding at zero), q <- q * rsqrt(sum(q^2) /
+// q_count + eps) * q_weight, q_count the true number of entries and q_weight one float per laid-out entry; the same
+// for k.  Then the first `rotary` entries of every q and k head rotate by halves (entry i with i + rotary / 2, angle
+// position * inv_freq[i], sine and cosine formed here in float32), q goes to q_out and k, v into the pages.
+// One block per token; the sums run down the block's fixed tree, so a token's result does not depend on the step.
+// All arithmetic float32, one rounding at the store.  kv_dest null: the row holds queries only.
+template <typename T>
+__global__ void row_norm_rope_write_kernel(const T* __restrict__ qkv, int row_width, const float* __restrict__ q_weight,
+                                           const float* __restrict__ k_weight, const float* __restrict__ inv_freq,
+                                           const int* __restrict__ positions, const int* __restrict__ kv_dest,
+                                           T* __restrict__ q_out, T* __restrict__ cache, int hq, int hkv, int d,
+                                           int rotary, int q_count, int k_count, float eps, int page_size,
+                                           int num_pages, int* __restrict__ fault) {
+  __shared__ float scratch[32];
+  __shared__ float cs[kMaxHeadDim / 2], sn[kMaxHeadDim / 2];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int half = rotary >> 1;
+  const float pos = static_cast<float>(positions[t]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &sn[i], &cs[i]);
+  const T* row = qkv + static_cast<size_t>(t) * row_width;
+  const int q_width = hq * d, k_width = hkv * d;
+  pdl_wait();
+  float sum_q = 0.0f, sum_k = 0.0f;
+  for (int i = threadIdx.x; i < q_width; i += blockDim.x) {
+    const float v = to_float(row[i]);
+    sum_q += v * v;
+  }
+  if (kv_dest) {
+    for (int i = threadIdx.x; i < k_width; i += blockDim.x) {
+      const float v = to_float(row[q_width + i]);
+      sum_k += v * v;
+    }
+  }
+  sum_q = block_sum(sum_q, scratch);      // (its barriers also publish the sines and cosines)
+  const float inv_q = rsqrtf(sum_q / static_cast<float>(q_count) + eps);
+  T* qo = q_out + static_cast<size_t>(t) * q_width;
+  for (int idx = threadIdx.x; idx < q_width; idx += blockDim.x) {
+    const int i = idx % d;
+    float v = to_float(row[idx]) * inv_q * q_weight[idx];
+    if (i < rotary) {
+      const int other_at = i < half ? idx + half : idx - half;
+      const float other = to_float(row[other_at]) * inv_q * q_weight[other_at];
+      const int pair = i < half ? i : i - half;
+      v = i < half ? v * cs[pair] - other * sn[pair] : v * cs[pair] + other * sn[pair];
+    }
+    qo[idx] = from_float<T>(v);
+  }
+  if (!kv_dest) return;
+  sum_k = block_sum(sum_k, scratch);
+  const float inv_k = rsqrtf(sum_k / static_cast<float>(k_count) + eps);
+  const int dest = kv_dest[t];
+  const int page = dest / page_size, offset = dest - page * page_size;
+  if (dest < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(fault, kFaultPageId);
+    return;
+  }
+  const T* kr = row + q_width;
+  const T* vr = kr + k_width;
+  for (int idx = threadIdx.x; idx < k_width; idx += blockDim.x) {
+    const int head = idx / d, i = idx - head * d;
+    float v = to_float(kr[idx]) * inv_k * k_weight[idx];
+    if (i < rotary) {
+      const int other_at = i < half ? idx + half : idx - half;
+      const float other = to_float(kr[other_at]) * inv_k * k_weight[other_at];
+      const int pair = i < half ? i : i - half;
+      v = i < half ? v * cs[pair] - other * sn[pair] : v * cs[pair] + other * sn[pair];
+    }
+    cache[(((static_cast<size_t>(page) * 2) * hkv + head) * page_size + offset) * d + i] = from_float<T>(v);
+    cache[(((static_cast<size_t>(page) * 2 + 1) * hkv + head) * page_size + offset) * d + i] = vr[idx];
+  }
+}
+
 }  // namespace rl
+
+extern "C" int rl_row_norm_rope_write(int dtype, const void* qkv, int row_width, const float* q_weight,
+                                      const float* k_weight, const float* inv_freq, const int* positions,
+                                      const int* kv_dest, void* q_out, void* cache, int tokens, int hq, int hkv, int d,
+                                      int rotary, int q_count, int k_count, float eps, int page_size, int num_pages,
+                                      int* fault, int pdl, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (d <= 0 || d > rl::kMaxHeadDim || rotary < 0 || rotary > d || (rotary & 1) || hq <= 0 || q_count < 1 ||
+      q_weight == nullptr || (rotary > 0 && inv_freq == nullptr) ||
+      (kv_dest != nullptr && (hkv <= 0 || k_count < 1 || k_weight == nullptr || cache == nullptr || page_size <= 0)) ||
+      row_width < (kv_dest ? (hq + 2 * hkv) * d : hq * d))
+    return static_cast<int>(cudaErrorInvalidValue);
+  RL_DISPATCH_DTYPE(dtype, {
+    return rl::launch_kernel(rl::row_norm_rope_write_kernel<scalar_t>, dim3(tokens), dim3(256), 0, stream, pdl != 0,
+                             static_cast<const scalar_t*>(qkv), row_width, q_weight, k_weight, inv_freq, positions,
+                             kv_dest, static_cast<scalar_t*>(q_out), static_cast<scalar_t*>(cache), hq, hkv, d, rotary,
+                             q_count, k_count, eps, page_size, num_pages, fault);
+  });
+  return 0;
+}
 
 extern "C" int rl_rope_unit_write(int dtype, const float* in, int in_stride, const float* inv_freq,
                                   const int* positions, const int* kv_dest, const float* mix, float* first,

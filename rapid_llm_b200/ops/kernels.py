@@ -118,6 +118,12 @@ def core() -> ctypes.CDLL:
     if not _SIGNATURES_SET:
         lib.rl_embedding.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p]
         lib.rl_add_rmsnorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
+        lib.rl_layernorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                     c_float, c_float, c_int, c_float, c_int, c_void_p]
+        lib.rl_row_norm_rope_write.argtypes = [
+            c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p,
+        ]
         lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rl_clamped_glu.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]
         lib.rl_rope_unit_write.argtypes = [
@@ -146,7 +152,7 @@ def core() -> ctypes.CDLL:
         ]
         for name in (
             "rl_embedding", "rl_embedding_sum", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float", "rl_clamped_glu",
-            "rl_rope_unit_write",
+            "rl_rope_unit_write", "rl_layernorm", "rl_row_norm_rope_write",
             "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample",
         ):
             getattr(lib, name).restype = c_int
@@ -291,6 +297,71 @@ def join_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, 
     _check(core().rl_add_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), None,
                                  x.shape[0], x.shape[1], float(eps), 4, 1, None, None, int(PDL), _stream()), "join_rmsnorm")
     return out
+
+
+LAYERNORM_KEEP, LAYERNORM_STORE_SUM, LAYERNORM_STORE_NORM = 0, 1, 2
+
+
+def layernorm(x: torch.Tensor | None, residual: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
+              out: torch.Tensor, eps: float, *, residual_scale: float = 1.0, store: int = LAYERNORM_KEEP,
+              row_index: torch.Tensor | None = None, gain: float = 1.0) -> torch.Tensor:
+    """Layer norm with a mean: with ``r = x + residual_scale * residual`` (either may be ``None``; ``residual`` is the
+    float32 stream), ``n = (r - mean r) * rsqrt(var r + eps) * weight + bias``, the variance being the mean of the
+    squared deviations, float32 throughout; ``out = n * gain`` in the engine's dtype.  ``store``:
+    :data:`LAYERNORM_STORE_SUM` writes ``r`` back into ``residual``, :data:`LAYERNORM_STORE_NORM` writes ``n`` there
+    (a norm behind the sum, whose result is the stream's new value).  ``row_index`` (int32) picks the input rows."""
+    _need_cuda(x, residual, weight, bias, out, row_index)
+    _expect("weight", weight, torch.float32), _expect("bias", bias, torch.float32), _expect("residual", residual, torch.float32)
+    _expect("row_index", row_index, torch.int32)
+    _contig("x", x), _contig("residual", residual), _contig("out", out), _contig("weight", weight), _contig("bias", bias)
+    source = x if x is not None else residual
+    if source is None:
+        raise KernelError("layernorm: there is nothing to norm")
+    hidden = source.shape[-1]
+    rows = row_index.numel() if row_index is not None else source.shape[0]
+    if (weight.numel() != hidden or (bias is not None and bias.numel() != hidden) or out.shape != (rows, hidden)
+            or (x is not None and (x.dtype != out.dtype or (residual is not None and residual.shape != x.shape)))):
+        raise KernelError("layernorm: shapes or dtypes of x, residual, weight, bias and out do not agree")
+    if store != LAYERNORM_KEEP and (residual is None or row_index is not None):
+        raise KernelError("layernorm: storing needs the stream, and every row of it")
+    _check(core().rl_layernorm(dtype_tag(out.dtype), _ptr(x), _ptr(residual), _ptr(weight), _ptr(bias), _ptr(out),
+                               _ptr(row_index), rows, hidden, float(eps), float(residual_scale), int(store), float(gain),
+                               int(PDL), _stream()), f"layernorm(hidden={hidden})")
+    return out
+
+
+def row_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
+                        q_weight: torch.Tensor, k_weight: torch.Tensor | None, q_count: int, k_count: int,
+                        inv_freq: torch.Tensor | None, positions: torch.Tensor, eps: float, fault: torch.Tensor,
+                        kv_dest: torch.Tensor | None = None, cache: torch.Tensor | None = None,
+                        page_size: int = 1) -> torch.Tensor:
+    """RMS norm of q over ALL its heads at once (and of k likewise), ``q * rsqrt(sum(q^2) / q_count + eps) * q_weight``
+    with one weight per laid-out entry, then rotation by halves of the first ``2 len(inv_freq)`` entries of every q and
+    k head (angles ``position * inv_freq`` formed in float32), q to ``q_out``, k and v into the pages.  ``qkv`` is
+    ``[T, (Hq + 2 Hkv) D]``, or ``[T, Hq D]`` with ``kv_dest`` ``None`` (queries only)."""
+    _need_cuda(qkv, q_out, q_weight, k_weight, inv_freq, positions, fault, kv_dest, cache)
+    _contig("qkv", qkv), _contig("q_out", q_out), _contig("cache", cache), _contig("inv_freq", inv_freq)
+    for name, tensor in (("q_weight", q_weight), ("k_weight", k_weight), ("inv_freq", inv_freq)):
+        _expect(name, tensor, torch.float32), _contig(name, tensor)
+    _expect("positions", positions, torch.int32), _expect("kv_dest", kv_dest, torch.int32)
+    tokens, row_width = qkv.shape
+    heads_in = num_heads + 2 * num_kv_heads if kv_dest is not None else num_heads
+    if row_width != heads_in * head_dim or q_out.numel() != tokens * num_heads * head_dim or q_out.dtype != qkv.dtype:
+        raise KernelError("row_norm_rope_write: qkv or q_out do not fit the heads")
+    if q_weight.numel() != num_heads * head_dim or (kv_dest is not None and (k_weight is None or k_weight.numel() != num_kv_heads * head_dim)):
+        raise KernelError("row_norm_rope_write: one norm weight per laid-out entry of q (and of k)")
+    num_pages = 0
+    if kv_dest is not None:
+        if cache is None or cache.dtype != qkv.dtype or cache.shape[1:] != (2, num_kv_heads, page_size, head_dim):
+            raise KernelError("row_norm_rope_write: cache must be [pages, 2, kv_heads, page_size, head_dim] of qkv's dtype")
+        num_pages = cache.shape[0]
+    rotary = 0 if inv_freq is None else 2 * inv_freq.numel()
+    _check(core().rl_row_norm_rope_write(
+        dtype_tag(qkv.dtype), _ptr(qkv), row_width, _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), _ptr(positions),
+        _ptr(kv_dest), _ptr(q_out), _ptr(cache), tokens, num_heads, num_kv_heads, head_dim, rotary, int(q_count),
+        int(k_count), float(eps), page_size, num_pages, _ptr(fault), int(PDL), _stream()),
+        f"row_norm_rope_write(head_dim={head_dim})")
+    return q_out
 
 
 def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
@@ -1342,13 +1413,14 @@ def moe_lib() -> ctypes.CDLL:
     if _MOE_LIB is None:
         lib = load_library("moe")
         lib.rl_router_topk.argtypes = [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
+                                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rl_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
         lib.rl_moe_tile_rows.argtypes = [c_int]
         lib.rl_grouped_linear.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                          c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+                                          c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int,
+                                          c_void_p]
         lib.rl_moe_combine.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
-                                       c_int, c_void_p]
+                                       c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         for name in ("rl_router_topk", "rl_moe_plan", "rl_grouped_linear", "rl_moe_combine", "rl_moe_tile_rows"):
             getattr(lib, name).restype = c_int
         _MOE_LIB = lib
@@ -1372,14 +1444,27 @@ def moe_max_tiles(pairs: int, experts: int, wide: bool = False) -> int:
 
 def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int, ids: torch.Tensor,
                 weights: torch.Tensor, gates: torch.Tensor | None = None, scores: torch.Tensor | None = None,
-                bias: torch.Tensor | None = None, softmax_chosen: bool = False) -> None:
+                bias: torch.Tensor | None = None, softmax_chosen: bool = False, softmax_all: bool = False,
+                correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1) -> None:
     """``z = weight[:experts] @ x[t] (+ bias)`` in float32; ``ids[t]`` the ``top`` largest (ties: the lower index),
     ``weights[t]`` their ``sigmoid(z)``, or with ``softmax_chosen`` the softmax over the chosen ``z`` alone; rows of
-    ``weight`` behind the experts' are gates, ``gates[t, g] = sigmoid(.)``."""
-    _need_cuda(x, weight, ids, weights, gates, scores, bias)
+    ``weight`` behind the experts' are gates, ``gates[t, g] = sigmoid(.)``.
+
+    With ``softmax_all`` the scores are ``s = softmax(z)`` over all ``experts`` rows; the choice is made on
+    ``s + correction`` (one float per row) among the rows of the ``keep`` best of ``groups`` equal groups of
+    neighbouring rows (a group ranks by its largest corrected score; rows of the other groups count as minus
+    infinity), and the weights are the chosen rows' ``s`` divided by their sum (plus 1e-20)."""
+    _need_cuda(x, weight, ids, weights, gates, scores, bias, correction)
     _expect("bias", bias, torch.float32), _contig("bias", bias)
+    _expect("correction", correction, torch.float32), _contig("correction", correction)
     if bias is not None and bias.numel() != experts:
         raise KernelError("router_topk: one bias per expert")
+    if softmax_all and (softmax_chosen or bias is not None or groups < 1 or experts % groups or not 1 <= keep <= groups
+                        or top > keep * (experts // groups) or (correction is not None and correction.numel() != experts)):
+        raise KernelError("router_topk: softmax over all rows takes a correction per row and groups that divide the rows "
+                          "and leave at least `top` rows to choose from")
+    if not softmax_all and (correction is not None or groups != 1):
+        raise KernelError("router_topk: corrections and groups belong to the softmax over all rows")
     _expect("weight", weight, torch.float32), _expect("ids", ids, torch.int32), _expect("weights", weights, torch.float32)
     _expect("gates", gates, torch.float32), _expect("scores", scores, torch.float32)
     _contig("weight", weight), _contig("ids", ids), _contig("weights", weights), _contig("gates", gates), _contig("scores", scores)
@@ -1390,7 +1475,8 @@ def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int
         raise KernelError("router_topk: shapes do not agree")
     _check(moe_lib().rl_router_topk(dtype_tag(x.dtype), _ptr(x), _row_stride("x", x), _ptr(weight), hidden, experts, extra,
                                     top, _ptr(ids), _ptr(weights), _ptr(gates), _ptr(scores), tokens, _ptr(bias),
-                                    int(bool(softmax_chosen)), int(PDL), _stream()),
+                                    2 if softmax_all else int(bool(softmax_chosen)), _ptr(correction), int(groups),
+                                    int(keep), int(PDL), _stream()),
            "router_topk")
 
 
@@ -1412,10 +1498,16 @@ def moe_plan(ids: torch.Tensor, experts: int, sorted_pairs: torch.Tensor, place_
 
 def grouped_linear(a: torch.Tensor, weight: torch.Tensor, sorted_pairs: torch.Tensor, meta: torch.Tensor, *, top: int,
                    by_token: bool, max_tiles: int, pair_weight: torch.Tensor | None = None,
-                   out_act: torch.Tensor | None = None, out_y: torch.Tensor | None = None, wide: bool = False) -> None:
+                   out_act: torch.Tensor | None = None, out_y: torch.Tensor | None = None, wide: bool = False,
+                   clamp: tuple[float, float] | None = None) -> None:
     """Products over the pairs grouped by expert: ``weight [E, N or 2 N, K]``.  With ``out_act`` (engine dtype,
-    by place) the weight is gate rows then up rows and ``out_act = silu(w g) * (w u)`` with the pair's weight ``w``;
-    with ``out_y`` (float32, by pair) the plain product.  ``a`` rows are found by token (pair // top) or by place."""
+    by place) the weight is gate rows then up rows and ``out_act = silu(w g) * (w u)`` with the pair's weight ``w``,
+    or with ``clamp = (limit, alpha)`` the clamped unit ``g' sigmoid(alpha g') (u' + 1)``, ``g' = min(g, limit)``,
+    ``u' = clamp(u, -limit, limit)``; with ``out_y`` (float32, by pair) the plain product.  ``a`` rows are found by
+    token (pair // top) or by place."""
+    limit, alpha = (0.0, 0.0) if clamp is None else (float(clamp[0]), float(clamp[1]))
+    if clamp is not None and limit <= 0.0:
+        raise KernelError("grouped_linear: the clamped unit needs a positive limit")
     _need_cuda(a, weight, sorted_pairs, meta, pair_weight, out_act, out_y)
     _contig("weight", weight), _contig("out_act", out_act), _contig("out_y", out_y)
     _expect("pair_weight", pair_weight, torch.float32), _expect("out_y", out_y, torch.float32)
@@ -1427,14 +1519,21 @@ def grouped_linear(a: torch.Tensor, weight: torch.Tensor, sorted_pairs: torch.Te
         raise KernelError("grouped_linear: the result's width does not fit the weight")
     _check(moe_lib().rl_grouped_linear(dtype_tag(a.dtype), _ptr(a), _row_stride("a", a), _ptr(weight), _ptr(sorted_pairs),
                                        _ptr(meta), _ptr(pair_weight), int(top), int(by_token), n, a.shape[1], int(gated),
-                                       _ptr(out_act), _ptr(out_y), int(max_tiles), moe_tile_rows(wide), int(PDL), _stream()),
+                                       _ptr(out_act), _ptr(out_y), int(max_tiles), moe_tile_rows(wide), limit, alpha,
+                                       int(PDL), _stream()),
            "grouped_linear")
 
 
 def moe_combine(y: torch.Tensor, top: int, out: torch.Tensor, shared: torch.Tensor | None = None,
-                gate: torch.Tensor | None = None, weights: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[t] = sum_j (weights[t, j] *) y[t * top + j] (+ gate[t] * shared[t])``, float32 sums in the order of ``j``."""
-    _need_cuda(y, out, shared, gate, weights)
+                gate: torch.Tensor | None = None, weights: torch.Tensor | None = None, ids: torch.Tensor | None = None,
+                experts: int = 0, x: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[t] = sum_j (weights[t, j] *) y[t * top + j] (+ gate[t] * shared[t])``, float32 sums in the order of ``j``.
+    With ``ids [T, top]`` and ``x [T, hidden]`` (the experts' input): a choice whose id is ``experts`` or more is an
+    identity expert, whose result is the token's own row ``x[t]`` (its row of ``y`` is never read)."""
+    _need_cuda(y, out, shared, gate, weights, ids, x)
+    _expect("ids", ids, torch.int32), _contig("ids", ids)
+    if (ids is None) != (x is None) or (ids is not None and (ids.numel() != y.shape[0] or x.shape != out.shape or x.dtype != out.dtype)):
+        raise KernelError("moe_combine: identity experts need the choices' ids and the experts' input rows")
     _expect("weights", weights, torch.float32), _contig("weights", weights)
     if weights is not None and weights.numel() != y.shape[0]:
         raise KernelError("moe_combine: one weight per (token, choice)")
@@ -1445,7 +1544,8 @@ def moe_combine(y: torch.Tensor, top: int, out: torch.Tensor, shared: torch.Tens
         raise KernelError("moe_combine: shapes do not agree")
     _check(moe_lib().rl_moe_combine(dtype_tag(out.dtype), _ptr(y), int(top), _ptr(shared), _ptr(gate),
                                     0 if gate is None else _row_stride("gate", gate), _ptr(out), tokens, hidden,
-                                    _ptr(weights), int(PDL), _stream()), "moe_combine")
+                                    _ptr(weights), _ptr(ids), int(experts), _ptr(x),
+                                    0 if x is None else _row_stride("x", x), int(PDL), _stream()), "moe_combine")
     return out
 
 

@@ -31,6 +31,13 @@ denominator, without a key or a value; ``value_mix`` blends a layer's values wit
 such layer of the model for the same tokens (``"first"`` leaves them in a buffer of the step,
 ``"later"`` reads them: ``v <- (1 - m) v + m v_first`` with the learned number ``m``), and the blended
 values are what is cached.
+
+``qk_norm_over="row"`` norms q (and k) over the WHOLE projection at once, before it is split into heads:
+``q <- q * rsqrt(mean(q^2) + eps) * w`` with the mean over all ``heads * head_dim`` entries and one weight per
+entry; rotation angles then come from frequencies (position kind ``rotary_frequencies``), and norm, rotation and the
+cache's store are one kernel.  ``cache_window`` says how many positions the layer's pages must keep when that differs
+from its own ``window``: a layer whose cache another layer reads with a wider window (or without one: 0) keeps what
+that reader needs.
 """
 
 from __future__ import annotations
@@ -206,6 +213,8 @@ class GQAAttention(Mixer):
         softcap: float = 0.0,
         sink: bool = False,
         value_mix: str | None = None,
+        qk_norm_over: str = "head",
+        cache_window: int | None = None,
         dtype,
         device,
     ) -> None:
@@ -220,8 +229,11 @@ class GQAAttention(Mixer):
             raise ValueError(f"head sizes ({head_dim}, {value_dim}) must lie between 1 and 256")
         if gate not in (None, "sigmoid"):
             raise ValueError(f"unknown output gate {gate!r}")
-        if (qkv_bias or shares_cache) and (padded != self.qk_dim or padded != self.v_dim):
-            raise ValueError("padded head sizes are not combined with a bias or a shared cache")
+        if qkv_bias and (padded != self.qk_dim or padded != self.v_dim):
+            raise ValueError("padded head sizes are not combined with a bias")
+        if qk_norm_over not in ("head", "row"):
+            raise ValueError(f"qk_norm_over must be 'head' or 'row', got {qk_norm_over!r}")
+        self.row_norm = bool(qk_norm) and qk_norm_over == "row"
         self.gate = gate
         # Options of mixers whose q, k and v pass a short convolution: they take the float32 path between the
         # projection and the cache (convolution, rotation, a weightless norm after it, blended values).
@@ -234,6 +246,8 @@ class GQAAttention(Mixer):
         self.float_prelude = self.conv_width > 0 or self.unit_after_rotation or value_mix is not None
         if self.float_prelude and (qk_norm or qkv_bias or shares_cache):
             raise ValueError("the convolution path has no weighted q/k norm, bias or shared cache")
+        if self.row_norm and qkv_bias:
+            raise ValueError("the norm over the whole projection is not combined with a bias")
         if not 0 <= self.conv_width <= 16 or self.softcap < 0:
             raise ValueError("conv_width must lie between 0 and 16, softcap must not be negative")
         self.names = {name: name for name in (
@@ -245,6 +259,10 @@ class GQAAttention(Mixer):
         self.hq, self.hkv, self.d = int(num_heads), int(num_kv_heads), padded
         self.qk_norm, self.eps = bool(qk_norm), float(qk_norm_eps)
         self.window = int(window)
+        # what the pages must keep: the layer's own window, unless a reader of its cache needs more (0 = everything)
+        self.cache_window = self.window if cache_window is None else int(cache_window)
+        if self.cache_window < 0 or (self.cache_window and (self.window == 0 or self.cache_window < self.window)):
+            raise ValueError(f"cache_window ({cache_window}) must cover the layer's own window ({window})")
         self.scale = float(scale) if scale is not None else self.qk_dim**-0.5
         self.shares_cache = bool(shares_cache)
         device = torch.device(device)
@@ -262,22 +280,24 @@ class GQAAttention(Mixer):
         self.qkv = self.new_storage((self.hq * self.d + kv_rows, self.hidden), MATRIX)
         self.o = self.new_storage((self.hidden, self.hq * self.d), MATRIX)
         self.qkv_bias = self.new_storage((self.qkv.shape[0],), VECTOR) if qkv_bias else None
-        self.q_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm else None
-        self.k_norm = self.new_storage((self.d,), VECTOR) if self.qk_norm and not self.shares_cache else None
+        # a norm over the whole projection has a weight per laid-out entry (zero in a head's padding)
+        norm_rows = (self.hq * self.d, self.hkv * self.d) if self.row_norm else (self.d, self.d)
+        self.q_norm = self.new_storage((norm_rows[0],), VECTOR) if self.qk_norm else None
+        self.k_norm = self.new_storage((norm_rows[1],), VECTOR) if self.qk_norm and not self.shares_cache else None
         self.g = self.new_storage((self.hq * self.d, self.hidden), MATRIX) if self.gate else None
         self.taps = self.new_storage((self.qkv.shape[0], self.conv_width), VECTOR) if self.conv_width > 0 else None
         self.sink = self.new_storage((self.hq,), VECTOR) if self.has_sink else None
         self.mix = self.new_storage((1,), VECTOR) if self.value_mix else None
         self.inv_freq = None
-        if self.float_prelude and self.rotary_dim > 0:
+        if (self.float_prelude or self.row_norm) and self.rotary_dim > 0:
             if not hasattr(self.position, "inv_freq"):
-                raise ValueError("the convolution path computes its angles from frequencies: position kind 'rotary_frequencies'")
+                raise ValueError("this path computes its angles from frequencies: position kind 'rotary_frequencies'")
             self.inv_freq = self.position.inv_freq
 
     # -- needs ----------------------------------------------------------------- #
     def cache_need(self) -> CacheNeed | None:
-        kind = "window" if self.window > 0 else "full"
-        return CacheNeed(kind, self.hkv, self.d, self.window)
+        kind = "window" if self.cache_window > 0 else "full"
+        return CacheNeed(kind, self.hkv, self.d, self.cache_window)
 
     def state_need(self) -> StateNeed | None:
         """The convolution's last ``conv_width - 1`` inputs (projected q, k, v) per request, float32."""
@@ -303,9 +323,10 @@ class GQAAttention(Mixer):
             for name in ("q_proj", "k_proj", "v_proj")[: 1 if self.shares_cache else 3]:
                 specs[f"{name}.bias"] = TensorSpec((specs[f"{name}.weight"].shape[0],), VECTOR)
         if self.qk_norm:
-            specs["q_norm.weight"] = TensorSpec((self.qk_dim,), VECTOR, init="ones_normal")
+            q_count, k_count = (self.hq * self.qk_dim, self.hkv * self.qk_dim) if self.row_norm else (self.qk_dim, self.qk_dim)
+            specs["q_norm.weight"] = TensorSpec((q_count,), VECTOR, init="ones_normal")
             if not self.shares_cache:
-                specs["k_norm.weight"] = TensorSpec((self.qk_dim,), VECTOR, init="ones_normal")
+                specs["k_norm.weight"] = TensorSpec((k_count,), VECTOR, init="ones_normal")
         if self.gate:
             specs["g_proj.weight"] = TensorSpec((self.hq * self.v_dim, self.hidden))
         if self.conv_width > 0:
@@ -356,6 +377,10 @@ class GQAAttention(Mixer):
             self.sink.copy_(tensor.to(torch.float32))
         elif name == "value_mix":
             self.mix.copy_(tensor.to(torch.float32).reshape(1))
+        elif name == "q_norm.weight" and self.row_norm:
+            self.q_norm.view(self.hq, self.d)[:, : self.qk_dim].copy_(tensor.to(torch.float32).view(self.hq, self.qk_dim))
+        elif name == "k_norm.weight" and self.row_norm:
+            self.k_norm.view(self.hkv, self.d)[:, : self.qk_dim].copy_(tensor.to(torch.float32).view(self.hkv, self.qk_dim))
         elif name == "q_norm.weight":
             self.q_norm[: self.qk_dim].copy_(tensor.to(torch.float32))
         elif name == "k_norm.weight":
@@ -394,6 +419,13 @@ class GQAAttention(Mixer):
         q = batch.workspace.get("attn_q", rows, self.hq * self.d, x.dtype)
         if self.float_prelude:
             self._float_prelude(qkv, q, batch, cache, group)
+        elif self.row_norm:
+            kernels.row_norm_rope_write(
+                qkv, q, num_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.d, q_weight=self.q_norm,
+                k_weight=self.k_norm, q_count=self.hq * self.qk_dim, k_count=self.hkv * self.qk_dim,
+                inv_freq=self.inv_freq, positions=batch.positions, eps=self.eps, fault=batch.fault,
+                kv_dest=group.kv_dest if cache.writes else None, cache=cache.pages if cache.writes else None,
+                page_size=group.page_size)
         else:
             self._norm_rope_write(qkv, q, batch, cache, group)
         attended = batch.workspace.get("attn_out", rows, self.hq * self.d, x.dtype)

@@ -15,6 +15,9 @@ sublayers read the stream itself; the stream is the float32 ``residual`` and ``x
 
 ``sandwich`` (:class:`SandwichBlock`): a norm on both sides of each sublayer,
 ``h' = h + NormB(Mixer(NormA(h))); h'' = h' + NormD(FeedForward(NormC(h')))``, the stream float32 in ``residual``.
+
+``postnorm`` (:class:`PostNormBlock`): the norm behind the sum, ``h' = Norm(alpha h + Mixer(h));
+h'' = Norm(alpha h' + FeedForward(h'))``; the stream is the norm's own result, float32 in ``residual``.
 """
 
 from __future__ import annotations
@@ -244,3 +247,42 @@ class SandwichBlock(PreNormBlock):
         normed = self._close(mixed, self.mixer_out_norm, residual, batch, self.feed_forward_norm).rows
         wide = self.feed_forward.forward(normed, batch)
         return self._close(wide, self.feed_forward_out_norm, residual, batch, after), residual
+
+
+@BLOCKS.register("postnorm")
+class PostNormBlock(PreNormBlock):
+    """The norm behind the sum: ``h <- Norm1(alpha * h + Mixer(h)); h <- Norm2(alpha * h + FeedForward(h))``.
+
+    The sublayers read the stream itself.  The stream lives in ``residual`` (float32): one kernel forms
+    ``alpha * stream + y`` for a sublayer's result ``y``, norms it, stores the norm as the stream's new value and
+    writes its rounding to the engine's dtype, which is what the next sublayer reads; ``x`` is that rounding.
+    ``alpha`` comes from the layer's ``arrangement_params`` (default 1).  The norm kind must offer ``post_join``
+    (``layernorm``)."""
+
+    stream_in_residual = True
+    NAMES = {"mixer_norm": "norm1", "mixer": "mix.", "feed_forward_norm": "norm2", "feed_forward": "mlp."}
+
+    def __init__(self, *, layer: LayerSpec, dtype, device, names: dict[str, str] | None = None) -> None:
+        super().__init__(layer=layer, dtype=dtype, device=device, names=names)
+        self.alpha = float((layer.arrangement_params or {}).get("alpha", 1.0))
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "post_join"):
+                raise ValueError("the postnorm arrangement needs norms that can close a sum (kind 'layernorm')")
+
+    def leading_norm(self):
+        return None
+
+    def forward(self, x, residual, batch, cache, then_norm=None, addend=None):
+        if addend is not None or isinstance(x, ScaledRows):
+            raise ValueError("this arrangement takes plain rows and no addend")
+        if residual is None:       # the embedding did not open the stream: it starts as x
+            residual = batch.workspace.get("residual", x.shape[0], x.shape[1], torch.float32)
+            kernels.to_float(x, residual)
+        mixed = self.mixer.forward(x, batch, cache)
+        gemm.flush()
+        x = self.mixer_norm.post_join(mixed, residual, self.alpha, batch)
+        if self.feed_forward is not None:
+            wide = self.feed_forward.forward(x, batch)
+            gemm.flush()
+            x = self.feed_forward_norm.post_join(wide, residual, self.alpha, batch)
+        return x, residual

@@ -17,7 +17,9 @@ one plane).  The zero-padded columns and the ``k_r`` columns of the attended row
 Options: ``rotation`` ``"halves"`` (entry ``i`` pairs with ``i + rot / 2``) or ``"neighbours"`` (``2i`` with
 ``2i + 1``); the nested position part gives the frequencies (``rotary_frequencies``, or ``yarn_frequencies`` with its
 magnitude on cosine and sine); ``head_gate`` multiplies head ``h``'s output by ``sigmoid(W_g x)_h``, one number per
-head from the mixer's input.  Norms, rotation and the gate are float32; the softmax is float32 in the attention kernels.
+head from the mixer's input; ``wide_gate`` multiplies the heads side by side, entry by entry, by ``sigmoid(W_g x)``
+(``heads * value_dim`` numbers from the mixer's input).  With ``q_rank=None`` there is no query latent: ``q = W_q x``
+directly (tensor ``q``).  Norms, rotation and the gates are float32; the softmax is float32 in the attention kernels.
 """
 
 from __future__ import annotations
@@ -36,21 +38,24 @@ def _up8(count: int) -> int:
 
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
-    DEFAULT_NAMES = ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "g", "o")
+    DEFAULT_NAMES = ("dq", "dq.norm", "uq", "q", "dkv", "dkv.norm", "uk", "uv", "g", "o")
 
     def __init__(self, *, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int, kv_rank: int,
-                 q_rank: int, scale: float, norm_eps: float, position: PartSpec, rotation: str = "halves",
-                 head_gate: bool = False, names: dict[str, str] | None = None, dtype, device) -> None:
+                 q_rank: int | None, scale: float, norm_eps: float, position: PartSpec, rotation: str = "halves",
+                 head_gate: bool = False, wide_gate: bool = False, names: dict[str, str] | None = None, dtype, device) -> None:
         super().__init__(dtype=dtype, device=device)
         if rotation not in ("halves", "neighbours"):
             raise ValueError(f"rotation must be 'halves' or 'neighbours', got {rotation!r}")
         self.hidden, self.h = int(hidden_size), int(num_heads)
         self.dim, self.rot, self.vdim = int(head_dim), int(rot_dim), int(value_dim)
-        self.kv_rank, self.q_rank = int(kv_rank), int(q_rank)
+        self.kv_rank, self.q_rank = int(kv_rank), int(q_rank or 0)
+        self.direct_q = q_rank is None        # no query latent: the queries are a product of the mixer's input
         self.scale, self.eps = float(scale), float(norm_eps)
         self.layout = kernels.ROTATE_HALVES if rotation == "halves" else kernels.ROTATE_NEIGHBOURS
-        self.has_gate = bool(head_gate)
-        if min(self.h, self.dim, self.vdim, self.kv_rank, self.q_rank) < 1 or self.rot < 0 or self.rot % 2:
+        self.has_gate, self.wide_gate = bool(head_gate), bool(wide_gate)
+        if self.has_gate and self.wide_gate:
+            raise ValueError("latent attention: a gate per head or a gate per entry, not both")
+        if min(self.h, self.dim, self.vdim, self.kv_rank, 1 if self.direct_q else self.q_rank) < 1 or self.rot < 0 or self.rot % 2:
             raise ValueError("latent attention: sizes must be positive and the rotated size even")
         self.d = -(-(self.kv_rank + self.rot) // 16) * 16          # a cached row, and a query as the attention sees it
         if self.d > 256:
@@ -73,7 +78,8 @@ class LatentAttention(Mixer):
         self.down = self.new_storage((self.down_rows, self.hidden), MATRIX)
         self.q_norm = self.new_storage((self.q_rank,), VECTOR)
         self.c_norm = self.new_storage((self.kv_rank,), VECTOR)
-        self.uq = self.new_storage((self.h * (self.dim + self.rot), self.q_rank), MATRIX)
+        self.uq = self.new_storage((self.h * (self.dim + self.rot), self.hidden if self.direct_q else self.q_rank), MATRIX)
+        self.g = self.new_storage((self.h * self.vdim, self.hidden), MATRIX) if self.wide_gate else None
         self.uk_t = self.new_storage((self.h, self.kv_rank, self.dim), MATRIX)      # W_uk_h^T: plain query -> latent
         self.uv = self.new_storage((self.h, self.vdim, self.kv_rank), MATRIX)
         self.o = self.new_storage((self.hidden, self.h * self.vdim), MATRIX)
@@ -90,7 +96,7 @@ class LatentAttention(Mixer):
         return self._items if self.dtype == torch.bfloat16 else None
 
     def uses_libraries(self) -> set[str]:
-        found = {"latent"}
+        found = {"latent"} | ({"recurrent"} if self.wide_gate else set())
         if self.dtype == torch.bfloat16:
             from ..ops.build import attention_library
             found |= {"gemm", attention_library(self.d)}
@@ -108,8 +114,13 @@ class LatentAttention(Mixer):
             "uv": TensorSpec((self.h * self.vdim, self.kv_rank)),
             "o": TensorSpec((self.hidden, self.h * self.vdim)),
         }
+        if self.direct_q:
+            del specs["dq"], specs["dq.norm"], specs["uq"]
+            specs["q"] = TensorSpec((self.h * (self.dim + self.rot), self.hidden))
         if self.has_gate:
             specs["g"] = TensorSpec((self.h, self.hidden))
+        if self.wide_gate:
+            specs["g"] = TensorSpec((self.h * self.vdim, self.hidden))
         return {self.names[name]: spec for name, spec in specs.items()}
 
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
@@ -120,6 +131,10 @@ class LatentAttention(Mixer):
             self.down[self.c_col0 : self.c_col0 + self.kv_rank + self.rot].copy_(tensor)
         elif name == "g" and self.has_gate:
             self.down[self.g_col0 : self.g_col0 + self.h].copy_(tensor)
+        elif name == "g" and self.wide_gate:
+            self.g.copy_(tensor)
+        elif name == "q" and self.direct_q:
+            self.uq.copy_(tensor)
         elif name == "dq.norm":
             self.q_norm.copy_(tensor.to(torch.float32))
         elif name == "dkv.norm":
@@ -136,12 +151,12 @@ class LatentAttention(Mixer):
             raise KeyError(name)
 
     def parameter_bytes(self) -> int:
-        matrices = (self.down, self.uq, self.uk_t, self.uv, self.o)
+        matrices = (self.down, self.uq, self.uk_t, self.uv, self.o) + (() if self.g is None else (self.g,))
         return sum(m.numel() for m in matrices) * self.down.element_size() + (self.q_rank + self.kv_rank) * 4
 
     def workspace_elements_per_token(self) -> int:
         return (self.down_rows + self.q_rank + self.h * (self.dim + self.rot) + 2 * self.h * self.d
-                + self.h * self.vdim + self.hidden)
+                + (3 if self.wide_gate else 1) * self.h * self.vdim + self.hidden)
 
     # -- forward --------------------------------------------------------------- #
     def forward(self, x, batch, cache):
@@ -151,12 +166,12 @@ class LatentAttention(Mixer):
         pages = cache.pages                                       # [pages, page_size, D]
         down = gemm.linear(x, self.down, space.get("latent_down", rows, self.down_rows, x.dtype), batch.fault)
         gemm.flush()
-        c_q = space.get("latent_cq", rows, self.q_rank, x.dtype)
+        c_q = space.get("latent_cq", rows, self.q_rank, x.dtype)      # no columns without a query latent
         kernels.latent_norm_write(
             down, q_col0=0, q_rank=self.q_rank, c_col0=self.c_col0, kv_rank=self.kv_rank, rot=self.rot,
             q_weight=self.q_norm, c_weight=self.c_norm, eps=self.eps, q_out=c_q, cache=pages, kv_dest=group.kv_dest,
             positions=batch.positions, freq=self.freq, magnitude=self.magnitude, layout=self.layout, fault=batch.fault)
-        q = gemm.linear(c_q, self.uq, space.get("latent_q", rows, self.uq.shape[0], x.dtype), batch.fault)
+        q = gemm.linear(x if self.direct_q else c_q, self.uq, space.get("latent_q", rows, self.uq.shape[0], x.dtype), batch.fault)
         gemm.flush()
         wide = space.get("latent_wide", rows, self.h * self.d, x.dtype)
         gemm.heads_linear(q, self.uk_t, wide)                  # columns [0, kv_rank) of every head
@@ -169,6 +184,11 @@ class LatentAttention(Mixer):
         gemm.heads_linear(attended, self.uv, values)
         if self.has_gate:
             kernels.sigmoid_scale_heads(values, down[:, self.g_col0 :], heads=self.h)
+        if self.wide_gate:
+            gate = gemm.linear(x, self.g, space.get("latent_gate", rows, self.h * self.vdim, x.dtype), batch.fault)
+            gemm.flush()
+            values = kernels.gated_norm(values, space.get("latent_gated", rows, self.h * self.vdim, x.dtype),
+                                        group=self.h * self.vdim, gate=gate, act=kernels.GATE_SIGMOID, norm=False)
         return gemm.linear(values, self.o, space.get("latent_out", rows, self.hidden, x.dtype), batch.fault)
 
     def _attend(self, q, pages, out, batch, group) -> None:

@@ -12,6 +12,14 @@ Two more options: ``router_bias`` adds a learned number per expert to ``z`` befo
 the weight multiplies the expert's result instead, ``y = sum_e w_e Expert_e(x)``, in the float32 sum over a
 token's choices.
 
+``weighting="softmax_all"`` is a third router: ``s = softmax(z)`` over all router rows; the choice is made on
+``s + correction`` (a learned number per row, tensor ``correction``) and only among the rows of the ``group_keep``
+best of ``num_groups`` equal groups of neighbouring rows (a group ranks by its largest corrected score); the weights
+are the chosen rows' ``s`` divided by their sum.  ``identity_experts`` appends that many router rows without tensors:
+an identity expert's result is its input, so a token that chooses one gets ``weight * x`` from it (the rows take part
+in the softmax and in the groups like any other).  ``expert_limit`` makes the experts clamped units,
+``down(g' * sigmoid(expert_alpha * g') * (u' + 1))`` with ``g' = min(gate x, limit)``, ``u' = clamp(up x, +-limit)``.
+
 The step's (token, expert) pairs are grouped by expert on the device (no host round trip, so a decode
 step is captured into a graph like any other), the two products run over the groups
 (``ops.kernels.grouped_linear``), and a last kernel sums a token's experts in the order of its choices.
@@ -34,16 +42,35 @@ class RoutedExperts(FeedForward):
                  expert_prefix: str = "e", router_name: str = "router", shared_prefix: str = "shared.",
                  shared_gate_name: str = "sg", gate_name: str = "gate", up_name: str = "up", down_name: str = "down",
                  router_bias: bool = False, router_bias_name: str = "router.b", weighting: str = "sigmoid",
+                 correction_name: str = "correction", num_groups: int = 1, group_keep: int = 1,
+                 identity_experts: int = 0, expert_limit: float | None = None, expert_alpha: float = 1.702,
                  dtype, device) -> None:
         super().__init__(dtype=dtype, device=device)
         self.hidden, self.experts, self.top, self.inter = int(hidden_size), int(num_experts), int(top_k), int(expert_size)
-        if not 1 <= self.top <= self.experts:
+        if not 1 <= self.top <= self.experts + int(identity_experts):
             raise ValueError(f"top_k ({top_k}) must lie between 1 and the number of experts ({num_experts})")
         if shared_gate and not shared_size:
             raise ValueError("a shared gate needs a shared expert")
-        if weighting not in ("sigmoid", "softmax_chosen"):
-            raise ValueError(f"unknown weighting {weighting!r}: 'sigmoid' or 'softmax_chosen'")
+        if weighting not in ("sigmoid", "softmax_chosen", "softmax_all"):
+            raise ValueError(f"unknown weighting {weighting!r}: 'sigmoid', 'softmax_chosen' or 'softmax_all'")
         self.scale_input, self.softmax_chosen = bool(scale_input), weighting == "softmax_chosen"
+        self.softmax_all = weighting == "softmax_all"
+        self.identity, self.groups, self.keep = int(identity_experts), int(num_groups), int(group_keep)
+        self.rows = self.experts + self.identity              # router rows a token chooses among
+        if not self.softmax_all and (self.identity or self.groups != 1):
+            raise ValueError("identity experts and groups belong to weighting 'softmax_all'")
+        if self.softmax_all:
+            if self.scale_input or router_bias:
+                raise ValueError("weighting 'softmax_all' weighs the experts' results and has no bias on the logits")
+            if self.identity < 0 or self.groups < 1 or self.rows % self.groups or not 1 <= self.keep <= self.groups:
+                raise ValueError(f"{self.groups} groups must divide the {self.rows} router rows, and 1 <= keep <= groups")
+            if not 1 <= self.top <= self.keep * (self.rows // self.groups):
+                raise ValueError(f"top_k ({top_k}) exceeds the rows of the {self.keep} groups a token may choose from")
+        self.clamp = None if expert_limit is None else (float(expert_limit), float(expert_alpha))
+        if self.clamp is not None and self.clamp[0] <= 0:
+            raise ValueError("expert_limit must be positive")
+        self.correction_name = correction_name
+        self.correction = self.new_storage((self.rows,), VECTOR) if self.softmax_all else None
         self.router_bias_name = router_bias_name
         self.bias = self.new_storage((self.experts,), VECTOR) if router_bias else None
         self.expert_prefix, self.router_name = expert_prefix, router_name
@@ -53,7 +80,7 @@ class RoutedExperts(FeedForward):
         self.down = self.new_storage((self.experts, self.hidden, self.inter), MATRIX)
         # router rows, then the shared expert's gate row: one float32 matrix for the router kernel
         self.has_gate = bool(shared_gate)
-        self.router = self.new_storage((self.experts + int(self.has_gate), self.hidden), VECTOR)
+        self.router = self.new_storage((self.rows + int(self.has_gate), self.hidden), VECTOR)
         self.shared = None
         if shared_size:
             self.shared = SwiGLU(hidden_size=self.hidden, intermediate_size=int(shared_size), dtype=dtype, device=device,
@@ -68,7 +95,9 @@ class RoutedExperts(FeedForward):
             specs[prefix + gate] = TensorSpec((self.inter, self.hidden))
             specs[prefix + up] = TensorSpec((self.inter, self.hidden))
             specs[prefix + down] = TensorSpec((self.hidden, self.inter))
-        specs[self.router_name] = TensorSpec((self.experts, self.hidden), VECTOR)
+        specs[self.router_name] = TensorSpec((self.rows, self.hidden), VECTOR)
+        if self.correction is not None:
+            specs[self.correction_name] = TensorSpec((self.rows,), VECTOR)
         if self.bias is not None:
             specs[self.router_bias_name] = TensorSpec((self.experts,), VECTOR)
         if self.shared is not None:
@@ -81,7 +110,10 @@ class RoutedExperts(FeedForward):
     def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
         gate, up, down = self.part_names
         if name == self.router_name:
-            self.router[: self.experts].copy_(tensor.to(torch.float32))
+            self.router[: self.rows].copy_(tensor.to(torch.float32))
+            return
+        if self.correction is not None and name == self.correction_name:
+            self.correction.copy_(tensor.to(torch.float32))
             return
         if self.bias is not None and name == self.router_bias_name:
             self.bias.copy_(tensor.to(torch.float32))
@@ -89,7 +121,7 @@ class RoutedExperts(FeedForward):
         if self.shared is not None and name.startswith(self.shared_prefix):
             rest = name[len(self.shared_prefix):]
             if self.has_gate and rest == self.shared_gate_name:
-                self.router[self.experts :].copy_(tensor.to(torch.float32))
+                self.router[self.rows :].copy_(tensor.to(torch.float32))
             else:
                 self.shared.load_tensor(rest, tensor)
             return
@@ -127,8 +159,9 @@ class RoutedExperts(FeedForward):
         ids = space.get("moe_ids", tokens, top, i32)
         weights = space.get("moe_weights", tokens, top, f32)
         gates = space.get("moe_gates", tokens, 1, f32) if self.has_gate else None
-        kernels.router_topk(x, self.router, experts=experts, top=top, ids=ids, weights=weights, gates=gates,
-                            bias=self.bias, softmax_chosen=self.softmax_chosen)
+        kernels.router_topk(x, self.router, experts=self.rows, top=top, ids=ids, weights=weights, gates=gates,
+                            bias=self.bias, softmax_chosen=self.softmax_chosen, softmax_all=self.softmax_all,
+                            correction=self.correction, groups=self.groups, keep=self.keep)
         order = space.get("moe_sorted", tokens, top, i32).view(-1)
         place = space.get("moe_place", tokens, top, i32).view(-1)
         wide = kernels.moe_wide_takes(x.dtype, self.hidden, self.inter)      # the pipelined bfloat16 tiles
@@ -137,10 +170,14 @@ class RoutedExperts(FeedForward):
         max_tiles = kernels.moe_plan(ids, experts, order, place, meta, batch.fault, wide=wide)
         act = space.get("moe_act", tokens, top * self.inter, x.dtype).view(pairs, self.inter)
         kernels.grouped_linear(x, self.gate_up, order, meta, top=top, by_token=True, max_tiles=max_tiles,
-                               pair_weight=weights.view(-1) if self.scale_input else None, out_act=act, wide=wide)
+                               pair_weight=weights.view(-1) if self.scale_input else None, out_act=act, wide=wide,
+                               clamp=self.clamp)
         each = space.get("moe_each", tokens, top * self.hidden, f32).view(pairs, self.hidden)
         kernels.grouped_linear(act, self.down, order, meta, top=top, by_token=False, max_tiles=max_tiles, out_y=each, wide=wide)
         shared = None if self.shared is None else self.shared.forward(x, batch)
         out = space.get("moe_out", tokens, self.hidden, x.dtype)
+        # pairs whose id lies behind the experts with tensors (identity experts) are in no tile of the plan: the sum
+        # takes the token's own row for them
         return kernels.moe_combine(each, top, out, shared=shared, gate=gates,
-                                   weights=None if self.scale_input else weights.view(-1))
+                                   weights=None if self.scale_input else weights.view(-1),
+                                   ids=ids if self.identity else None, experts=experts, x=x if self.identity else None)

@@ -1,4 +1,4 @@
-"""RMSNorm with the residual add folded in.
+"""Norms with the residual add folded in: RMSNorm, and the layer norm with a mean and a bias.
 
 ``y = r * rsqrt(mean(r^2) + eps) * w`` with ``r = x`` or ``r = x + residual``; the weight
 multiplies as ``w`` (with ``unit_offset`` the checkpoint stores ``w - 1``, a weight around zero, and one is added
@@ -83,3 +83,73 @@ class RMSNorm(Norm):
             extra_rows=None if addend is None else addend.rows,
             extra_vector=None if addend is None else addend.vector,
         )
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """``n = (r - mean r) / sqrt(var r + eps) * weight + bias``, the variance being the mean of the squared deviations;
+    float32 statistics, float32 weight and bias.  ``bias_suffix`` names the bias after the weight's own name
+    (``None``: no bias).  ``gain`` multiplies what the norm hands on (not what it stores in the stream): a model
+    whose head scales its logits by a constant gives that constant to its last norm, since
+    ``(W n) * gain = W (n * gain)`` and the product's input is rounded once either way.
+
+    Beside the interface of every norm (``forward`` with the modes of :mod:`parts.norm`) it has the two forms an
+    arrangement with the norm BEHIND the sum needs: :meth:`post_join` (``stream <- norm(alpha * stream + y)``) and
+    :meth:`of_stream`."""
+
+    reads_deferred = True
+
+    def __init__(self, *, size: int, eps: float, dtype, device, name: str = "weight", bias_suffix: str | None = ".b",
+                 gain: float = 1.0) -> None:
+        super().__init__(dtype=dtype, device=device)
+        self.size, self.eps, self.gain = int(size), float(eps), float(gain)
+        self.name = name
+        self.bias_name = None if bias_suffix is None else name + bias_suffix
+        self.weight = self.new_storage((self.size,), VECTOR)
+        self.bias = None if self.bias_name is None else self.new_storage((self.size,), VECTOR)
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        specs = {self.name: TensorSpec((self.size,), VECTOR, init="ones_normal")}
+        if self.bias_name is not None:
+            specs[self.bias_name] = TensorSpec((self.size,), VECTOR)
+        return specs
+
+    def load_tensor(self, name: str, tensor: torch.Tensor) -> None:
+        if name == self.name:
+            self.weight.copy_(tensor.to(torch.float32))
+        elif name == self.bias_name:
+            self.bias.copy_(tensor.to(torch.float32))
+        else:
+            raise KeyError(name)
+
+    def parameter_bytes(self) -> int:
+        return self.weight.numel() * 4 * (1 if self.bias is None else 2)
+
+    def workspace_elements_per_token(self) -> int:
+        return self.size
+
+    def post_join(self, y, residual, alpha: float, batch, name="stream_rows"):
+        """``residual <- norm(alpha * residual + y)`` in float32, in place; returns the new stream in the engine's
+        dtype (what the next sublayer reads)."""
+        out = batch.workspace.get(name, y.shape[0], self.size, y.dtype)
+        return kernels.layernorm(y, residual, self.weight, self.bias, out, self.eps, residual_scale=alpha,
+                                 store=kernels.LAYERNORM_STORE_NORM, gain=self.gain)
+
+    def of_stream(self, residual, batch, *, row_index=None, name="normed"):
+        """The norm of the float32 stream itself (rows picked by ``row_index``), in the engine's dtype."""
+        rows = residual.shape[0] if row_index is None else row_index.numel()
+        out = batch.workspace.get(name, rows, self.size, self.dtype, min_rows=None if row_index is None else 64)
+        return kernels.layernorm(None, residual, self.weight, self.bias, out, self.eps, row_index=row_index, gain=self.gain)
+
+    def forward(self, x, residual, batch, *, mode, write_residual, row_index=None, name="normed", addend=None):
+        if addend is not None:
+            raise ValueError("this norm takes no addend")
+        rows = x.shape[0] if row_index is None else row_index.numel()
+        out = batch.workspace.get(name, rows, self.size, x.dtype, min_rows=None if row_index is None else 64)
+        if mode == ADD:
+            store = kernels.LAYERNORM_STORE_SUM if write_residual else kernels.LAYERNORM_KEEP
+            return kernels.layernorm(x, residual, self.weight, self.bias, out, self.eps, store=store, row_index=row_index,
+                                     gain=self.gain)
+        if mode == FIRST and write_residual:
+            kernels.to_float(x, residual)
+        return kernels.layernorm(x, None, self.weight, self.bias, out, self.eps, row_index=row_index, gain=self.gain)
