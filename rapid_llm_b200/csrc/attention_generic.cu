@@ -1,4 +1,5 @@
-// Paged causal attention for any head size (steps of 16 up to 256), any number of heads
+// Paged causal attention for any head size (steps of 16 up to 256; up to 640 in a second build of the
+// kernel with more registers, for cached latent rows wider than the tensor-core tiles take), any number of heads
 // and groups, any page size, with an optional window; one warp per (token, query head).
 //
 // This is the kernel of the float32 path and the fallback of the bfloat16 path for head
@@ -19,8 +20,9 @@ namespace rl {
 
 constexpr int kGenericWarps = 4;
 constexpr int kGenericMaxD = 256;
+constexpr int kGenericWideD = 640;
 
-template <typename T>
+template <typename T, int kMaxD>
 __global__ void attention_generic_kernel(
     const T* __restrict__ q,            // [tokens, hq, d]
     const T* __restrict__ cache,        // [num_pages, kv_planes (2, or 1: values are the keys' rows), hkv, page_size, d]
@@ -30,7 +32,7 @@ __global__ void attention_generic_kernel(
     const int* __restrict__ block_table,  // [slots, max_pages]
     int tokens, int hq, int hkv, int d, int page_size, int num_pages, int max_pages, int slots,
     int window, float scale, float softcap, const float* __restrict__ sink, int kv_planes, int* __restrict__ fault) {
-  __shared__ float q_staged[kGenericWarps][kGenericMaxD];
+  __shared__ float q_staged[kGenericWarps][kMaxD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * kGenericWarps + warp;
   if (item >= static_cast<long long>(tokens) * hq) return;
@@ -58,9 +60,9 @@ __global__ void attention_generic_kernel(
   const size_t v_offset = kv_planes == 2 ? static_cast<size_t>(hkv) * head_stride : 0;
 
   float running_max = -INFINITY, running_sum = 0.0f;
-  float acc[kGenericMaxD / 32];
+  float acc[kMaxD / 32];
 #pragma unroll
-  for (int i = 0; i < kGenericMaxD / 32; ++i) acc[i] = 0.0f;
+  for (int i = 0; i < kMaxD / 32; ++i) acc[i] = 0.0f;
 
   for (int base = first; base <= pos; base += 32) {
     const int j = base + lane;
@@ -94,7 +96,7 @@ __global__ void attention_generic_kernel(
     running_sum = running_sum * correction + warp_sum(p);
     running_max = new_max;
 #pragma unroll
-    for (int i = 0; i < kGenericMaxD / 32; ++i) acc[i] *= correction;
+    for (int i = 0; i < kMaxD / 32; ++i) acc[i] *= correction;
     const int count = min(32, pos - base + 1);
     for (int jj = 0; jj < count; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
@@ -102,7 +104,7 @@ __global__ void attention_generic_kernel(
       if (row < 0) continue;
       const T* vr = cache + row + v_offset;
 #pragma unroll
-      for (int i = 0; i < kGenericMaxD / 32; ++i) {
+      for (int i = 0; i < kMaxD / 32; ++i) {
         const int col = lane + 32 * i;
         if (col < d) acc[i] = fmaf(pj, to_float(vr[col]), acc[i]);
       }
@@ -117,7 +119,7 @@ __global__ void attention_generic_kernel(
     inv_sum = keys / (running_sum * keys + expf(s - top));
   }
 #pragma unroll
-  for (int i = 0; i < kGenericMaxD / 32; ++i) {
+  for (int i = 0; i < kMaxD / 32; ++i) {
     const int col = lane + 32 * i;
     if (col < d) o[col] = from_float<T>(acc[i] * inv_sum);
   }
@@ -132,14 +134,16 @@ extern "C" int rl_attention_generic(int dtype, const void* q, const void* cache,
                                     int window, float scale, float softcap, const float* sink, int kv_planes,
                                     int* fault, cudaStream_t stream) {
   if (tokens == 0) return 0;
-  if (d <= 0 || d % 16 != 0 || d > rl::kGenericMaxD || hkv <= 0 || hq % hkv != 0 ||
+  if (d <= 0 || d % 16 != 0 || d > rl::kGenericWideD || hkv <= 0 || hq % hkv != 0 ||
       page_size <= 0 || window < 0 || softcap < 0.0f || kv_planes < 1 || kv_planes > 2)
     return static_cast<int>(cudaErrorInvalidValue);
   const long long items = static_cast<long long>(tokens) * hq;
   const unsigned blocks =
       static_cast<unsigned>((items + rl::kGenericWarps - 1) / rl::kGenericWarps);
   RL_DISPATCH_DTYPE(dtype, {
-    rl::attention_generic_kernel<scalar_t><<<blocks, rl::kGenericWarps * 32, 0, stream>>>(
+    auto kernel = d <= rl::kGenericMaxD ? rl::attention_generic_kernel<scalar_t, rl::kGenericMaxD>
+                                        : rl::attention_generic_kernel<scalar_t, rl::kGenericWideD>;
+    kernel<<<blocks, rl::kGenericWarps * 32, 0, stream>>>(
         static_cast<const scalar_t*>(q), static_cast<const scalar_t*>(cache),
         static_cast<scalar_t*>(out), positions, token_slot, block_table, tokens, hq, hkv, d,
         page_size, num_pages, max_pages, slots, window, scale, softcap, sink, kv_planes, fault);

@@ -520,8 +520,8 @@ def attention_generic(
         raise KernelError("attention: q, cache and out must share a dtype")
     if cache.dim() != 5 or cache.shape[1] not in (1, 2) or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
         raise KernelError("attention: cache must be [pages, 2 (or 1: values are the keys' rows), kv_heads, page_size, head_dim]")
-    if head_dim % 16 or head_dim > 256:
-        raise KernelError(f"attention: head_dim {head_dim} must be a multiple of 16 up to 256")
+    if head_dim % 16 or head_dim > 640:
+        raise KernelError(f"attention: head_dim {head_dim} must be a multiple of 16 up to 640")
     _check(
         core().rl_attention_generic(
             dtype_tag(q.dtype), _ptr(q), _ptr(cache), _ptr(out), _ptr(positions), _ptr(token_slot),

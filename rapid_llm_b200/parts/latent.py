@@ -58,9 +58,12 @@ class LatentAttention(Mixer):
         if min(self.h, self.dim, self.vdim, self.kv_rank, 1 if self.direct_q else self.q_rank) < 1 or self.rot < 0 or self.rot % 2:
             raise ValueError("latent attention: sizes must be positive and the rotated size even")
         self.d = -(-(self.kv_rank + self.rot) // 16) * 16          # a cached row, and a query as the attention sees it
-        if self.d > 256:
+        # the tensor-core tiles take rows of up to 256 numbers; wider rows (up to 640) run the one-warp-per-row kernel
+        # in either precision
+        self.wide_row = self.d > 256
+        if self.d > 640:
             raise ValueError(f"latent attention: kv_rank + rot_dim = {self.kv_rank + self.rot} exceeds the attention "
-                             f"kernels' widest head (256)")
+                             f"kernels' widest row (640)")
         self.names = {name: name for name in self.DEFAULT_NAMES}
         self.names.update(names or {})
         self._ours = {theirs: ours for ours, theirs in self.names.items()}
@@ -93,13 +96,13 @@ class LatentAttention(Mixer):
         return CacheNeed("full", token_shape=(self.d,))
 
     def step_planner(self) -> StepPlanner | None:
-        return self._items if self.dtype == torch.bfloat16 else None
+        return self._items if self.dtype == torch.bfloat16 and not self.wide_row else None
 
     def uses_libraries(self) -> set[str]:
         found = {"latent"} | ({"recurrent"} if self.wide_gate else set())
         if self.dtype == torch.bfloat16:
             from ..ops.build import attention_library
-            found |= {"gemm", attention_library(self.d)}
+            found |= {"gemm"} | (set() if self.wide_row else {attention_library(self.d)})
         return found
 
     # -- weights --------------------------------------------------------------- #
@@ -192,7 +195,7 @@ class LatentAttention(Mixer):
         return gemm.linear(values, self.o, space.get("latent_out", rows, self.hidden, x.dtype), batch.fault)
 
     def _attend(self, q, pages, out, batch, group) -> None:
-        if q.dtype == torch.bfloat16:
+        if q.dtype == torch.bfloat16 and not self.wide_row:
             plan = batch.extras[self._items.key]
             splits = plan["splits"]
             part_out = part_lse = None

@@ -124,7 +124,7 @@ def clamped_expert(h, gate_w, up_w, down_w, limit: float) -> torch.Tensor:
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ down_w.T
 
 
-def route(h, router_w, correction, top: int, groups: int, keep: int):
+def route(h, router_w, correction, top: int, groups: int, keep: int, margins: list | None = None):
     """``(chosen [T, top], weights [T, top], scores [T, E])``: softmax over all router rows; the choice is made on
     scores plus ``correction`` among the rows of the ``keep`` best of ``groups`` equal groups of neighbours (a group's
     rank is its largest corrected score); weights are the chosen rows' plain scores over their sum."""
@@ -135,21 +135,28 @@ def route(h, router_w, correction, top: int, groups: int, keep: int):
         per = E // groups
         best = choice.view(T, groups, per).max(-1).values                   # [T, groups]
         kept = torch.topk(best, keep, dim=-1).indices
+        if margins is not None and keep < groups:
+            ranked = best.sort(-1, descending=True).values
+            margins.extend(((ranked[:, keep - 1] - ranked[:, keep]) / scores.std(-1)).tolist())
         allowed = torch.zeros(T, groups, dtype=torch.bool)
         allowed.scatter_(1, kept, True)
         choice = choice.masked_fill(~allowed.repeat_interleave(per, dim=1), -math.inf)
     chosen = torch.topk(choice, top, dim=-1).indices
+    if margins is not None and top < E:
+        ranked = choice.sort(-1, descending=True).values
+        gap = ranked[:, top - 1] - ranked[:, top]                            # infinite where no other row was allowed
+        margins.extend((gap / scores.std(-1)).tolist())
     picked = torch.gather(scores, 1, chosen)
     return chosen, picked / (picked.sum(-1, keepdim=True) + 1e-20), scores
 
 
-def routed_experts(h, tensors, prefix: str, mlp: dict) -> torch.Tensor:
+def routed_experts(h, tensors, prefix: str, mlp: dict, margins: list | None = None) -> torch.Tensor:
     router = mlp["router"]
     experts, identity, top = int(router["experts"]), int(router.get("identity", 0)), int(router["top"])
     groups = router.get("groups") or {}
     limit = float(mlp["expert"]["limit"])
     chosen, weights, _ = route(h, tensors[prefix + "router"], tensors[prefix + "correction"], top,
-                               int(groups.get("count", 1)), int(groups.get("keep", 1)))
+                               int(groups.get("count", 1)), int(groups.get("keep", 1)), margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, w in zip(chosen[t].tolist(), weights[t]):
@@ -163,8 +170,9 @@ def routed_experts(h, tensors, prefix: str, mlp: dict) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------- model -- #
-def forward(config: dict, tensors: dict, tokens, collect_layers: bool = False):
-    """Logits ``[T, vocab]`` of one sequence (and, with ``collect_layers``, the stream after every layer)."""
+def forward(config: dict, tensors: dict, tokens, collect_layers: bool = False, margins: list | None = None):
+    """Logits ``[T, vocab]`` of one sequence (and, with ``collect_layers``, the stream after every layer).  ``margins``
+    collects how clearly every router decision fell, in units of the scores' spread."""
     eps, alpha = float(config["norm"]["eps"]), float(config["postln_alpha"])
     x = tensors["embed"][torch.as_tensor(tokens)] * float(config["embedding"]["scale"])
     kept: dict[int, tuple] = {}
@@ -180,9 +188,25 @@ def forward(config: dict, tensors: dict, tokens, collect_layers: bool = False):
                                                  None if source is None else kept[int(source)])
         x = layer_norm(alpha * x + mixed, tensors[p + "norm1"], tensors[p + "norm1.b"], eps)
         if layer.get("mlp") is not None:
-            wide = routed_experts(x, tensors, p + "mlp.", layer["mlp"])
+            wide = routed_experts(x, tensors, p + "mlp.", layer["mlp"], margins)
             x = layer_norm(alpha * x + wide, tensors[p + "norm2"], tensors[p + "norm2.b"], eps)
         streams.append(x)
     x = layer_norm(x, tensors["final.norm"], tensors["final.norm.b"], eps)
     logits = x @ tensors["head"].T * float(config["logit_scale"])
     return (logits, torch.stack(streams)) if collect_layers else logits
+
+
+def greedy(config: dict, tensors: dict, tokens, steps: int) -> list[int]:
+    """The ``steps`` tokens that always taking the largest logit produces after ``tokens``."""
+    tokens = list(tokens)
+    start = len(tokens)
+    for _ in range(steps):
+        tokens.append(int(forward(config, tensors, tokens)[-1].argmax()))
+    return tokens[start:]
+
+
+def clear_margin(config: dict, tensors: dict, tokens) -> float:
+    """The narrowest router decision of the sequence (infinite for a model without routers)."""
+    margins: list = []
+    forward(config, tensors, tokens, margins=margins)
+    return min(margins) if margins else math.inf
