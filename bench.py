@@ -589,8 +589,8 @@ def main() -> int:
                         "benchmark's; 14b and 32b are the other shapes of the same architecture")
     parser.add_argument("--context", type=int, default=CONTEXT, help="longest sequence the engine is set up for")
     parser.add_argument("--points", default="1,64", help="other batch sizes decoded beside --batch")
-    parser.add_argument("--sizes", default="2048,4096", help="widths of the models of --workload kopatar, mezadra and basitar")
-    parser.add_argument("--workload", choices=["decode", "serve", "kopatar", "mezadra", "basitar"], default="decode", help="decode: the benchmark "
+    parser.add_argument("--sizes", default="2048,4096", help="widths of the models of --workload kopatar, mezadra, basitar and zupupel")
+    parser.add_argument("--workload", choices=["decode", "serve", "kopatar", "mezadra", "basitar", "zupupel"], default="decode", help="decode: the benchmark "
                         "(timed decode steps, a prefill, the points); serve: continuous batching of --requests "
                         "prompts of mixed lengths through generate()")
     parser.add_argument("--requests", type=int, default=64, help="requests of the serve workload")
@@ -642,6 +642,15 @@ def main() -> int:
 
         with ClockSampler() as clocks:
             result = basitar_run([int(size) for size in args.sizes.split(",") if size], measured_peaks()["hbm_gbs"])
+        result["clocks"] = clocks.summary()
+        print(json.dumps(result))
+        return 0
+    if args.workload == "zupupel":
+        # the design with windowed attention that shares caches, latent attention and grouped routing beside its closest models
+        from rapid_llm_b200.ops.zupupel_compare import run as zupupel_run
+
+        with ClockSampler() as clocks:
+            result = zupupel_run([int(size) for size in args.sizes.split(",") if size], measured_peaks()["hbm_gbs"])
         result["clocks"] = clocks.summary()
         print(json.dumps(result))
         return 0

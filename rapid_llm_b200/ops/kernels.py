@@ -346,8 +346,8 @@ def row_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: in
     _expect("positions", positions, torch.int32), _expect("kv_dest", kv_dest, torch.int32)
     tokens, row_width = qkv.shape
     heads_in = num_heads + 2 * num_kv_heads if kv_dest is not None else num_heads
-    if row_width != heads_in * head_dim or q_out.numel() != tokens * num_heads * head_dim or q_out.dtype != qkv.dtype:
-        raise KernelError("row_norm_rope_write: qkv or q_out do not fit the heads")
+    if row_width < heads_in * head_dim or q_out.numel() != tokens * num_heads * head_dim or q_out.dtype != qkv.dtype:
+        raise KernelError("row_norm_rope_write: qkv or q_out do not fit the heads")      # columns behind the heads are not read
     if q_weight.numel() != num_heads * head_dim or (kv_dest is not None and (k_weight is None or k_weight.numel() != num_kv_heads * head_dim)):
         raise KernelError("row_norm_rope_write: one norm weight per laid-out entry of q (and of k)")
     num_pages = 0

@@ -277,15 +277,21 @@ class GQAAttention(Mixer):
         self.rotary_dim = int(position.params.get("rotary_dim", getattr(self.position, "rotary_dim", self.d)))
 
         kv_rows = 0 if self.shares_cache else 2 * self.hkv * self.d
-        self.qkv = self.new_storage((self.hq * self.d + kv_rows, self.hidden), MATRIX)
+        # With the norm over the whole projection the gate's rows lie behind q, k and v in ONE matrix: one product
+        # reads the mixer's input once for all four, and the kernels behind it take rows wider than they use.
+        self.gate_rides = bool(self.gate) and self.row_norm
+        self.qkv_rows = self.hq * self.d + kv_rows
+        self.qkv = self.new_storage((self.qkv_rows + (self.hq * self.d if self.gate_rides else 0), self.hidden), MATRIX)
         self.o = self.new_storage((self.hidden, self.hq * self.d), MATRIX)
-        self.qkv_bias = self.new_storage((self.qkv.shape[0],), VECTOR) if qkv_bias else None
+        self.qkv_bias = self.new_storage((self.qkv_rows,), VECTOR) if qkv_bias else None
         # a norm over the whole projection has a weight per laid-out entry (zero in a head's padding)
         norm_rows = (self.hq * self.d, self.hkv * self.d) if self.row_norm else (self.d, self.d)
         self.q_norm = self.new_storage((norm_rows[0],), VECTOR) if self.qk_norm else None
         self.k_norm = self.new_storage((norm_rows[1],), VECTOR) if self.qk_norm and not self.shares_cache else None
-        self.g = self.new_storage((self.hq * self.d, self.hidden), MATRIX) if self.gate else None
-        self.taps = self.new_storage((self.qkv.shape[0], self.conv_width), VECTOR) if self.conv_width > 0 else None
+        self.g = None
+        if self.gate:
+            self.g = self.qkv[self.qkv_rows :] if self.gate_rides else self.new_storage((self.hq * self.d, self.hidden), MATRIX)
+        self.taps = self.new_storage((self.qkv_rows, self.conv_width), VECTOR) if self.conv_width > 0 else None
         self.sink = self.new_storage((self.hq,), VECTOR) if self.has_sink else None
         self.mix = self.new_storage((1,), VECTOR) if self.value_mix else None
         self.inv_freq = None
@@ -302,7 +308,7 @@ class GQAAttention(Mixer):
     def state_need(self) -> StateNeed | None:
         """The convolution's last ``conv_width - 1`` inputs (projected q, k, v) per request, float32."""
         if self.conv_width > 1:
-            return StateNeed(((self.conv_width - 1) * self.qkv.shape[0],), torch.float32)
+            return StateNeed(((self.conv_width - 1) * self.qkv_rows,), torch.float32)
         return None
 
     def step_planner(self) -> StepPlanner | None:
@@ -352,7 +358,7 @@ class GQAAttention(Mixer):
             self._heads(self.qkv[q_rows : q_rows + kv_rows], self.hkv)[:, : self.qk_dim].copy_(
                 tensor.view(self.hkv, self.qk_dim, -1))
         elif name == "v_proj.weight":
-            self._heads(self.qkv[q_rows + kv_rows :], self.hkv)[:, : self.v_dim].copy_(
+            self._heads(self.qkv[q_rows + kv_rows : self.qkv_rows], self.hkv)[:, : self.v_dim].copy_(
                 tensor.view(self.hkv, self.v_dim, -1))
         elif name == "o_proj.weight":
             self.o.view(self.hidden, self.hq, self.d)[:, :, : self.v_dim].copy_(
@@ -389,7 +395,7 @@ class GQAAttention(Mixer):
             raise KeyError(name)
 
     def parameter_bytes(self) -> int:
-        total = (self.qkv.numel() + self.o.numel() + (0 if self.g is None else self.g.numel())) * self.qkv.element_size()
+        total = (self.qkv.numel() + self.o.numel() + (0 if self.g is None or self.gate_rides else self.g.numel())) * self.qkv.element_size()
         for vector in (self.q_norm, self.k_norm, self.qkv_bias, self.taps, self.sink, self.mix):
             if vector is not None:
                 total += vector.numel() * 4
@@ -431,8 +437,11 @@ class GQAAttention(Mixer):
         attended = batch.workspace.get("attn_out", rows, self.hq * self.d, x.dtype)
         self.attend(q, cache.pages, attended, batch, group)
         if self.gate:
-            gate = batch.workspace.get("attn_gate", rows, self.hq * self.d, x.dtype)
-            gemm.linear(x, self.g, gate, batch.fault)
+            if self.gate_rides:
+                gate = qkv[:, self.qkv_rows :]          # the first product brought it along
+            else:
+                gate = batch.workspace.get("attn_gate", rows, self.hq * self.d, x.dtype)
+                gemm.linear(x, self.g, gate, batch.fault)
             gated = batch.workspace.get("attn_gated", rows, self.hq * self.d, x.dtype)
             attended = kernels.gated_norm(attended, gated, group=self.hq * self.d, gate=gate,
                                           act=kernels.GATE_SIGMOID, norm=False)

@@ -77,12 +77,12 @@ class LatentAttention(Mixer):
         # that is a multiple of 8
         self.c_col0 = _up8(self.q_rank)
         self.g_col0 = self.c_col0 + _up8(self.kv_rank + self.rot)
-        self.down_rows = self.g_col0 + (_up8(self.h) if self.has_gate else 0)
+        self.down_rows = self.g_col0 + (_up8(self.h) if self.has_gate else self.h * self.vdim if self.wide_gate else 0)
         self.down = self.new_storage((self.down_rows, self.hidden), MATRIX)
         self.q_norm = self.new_storage((self.q_rank,), VECTOR)
         self.c_norm = self.new_storage((self.kv_rank,), VECTOR)
         self.uq = self.new_storage((self.h * (self.dim + self.rot), self.hidden if self.direct_q else self.q_rank), MATRIX)
-        self.g = self.new_storage((self.h * self.vdim, self.hidden), MATRIX) if self.wide_gate else None
+        self.g = self.down[self.g_col0 :] if self.wide_gate else None      # the wide gate's rows, behind the latent's
         self.uk_t = self.new_storage((self.h, self.kv_rank, self.dim), MATRIX)      # W_uk_h^T: plain query -> latent
         self.uv = self.new_storage((self.h, self.vdim, self.kv_rank), MATRIX)
         self.o = self.new_storage((self.hidden, self.h * self.vdim), MATRIX)
@@ -154,12 +154,12 @@ class LatentAttention(Mixer):
             raise KeyError(name)
 
     def parameter_bytes(self) -> int:
-        matrices = (self.down, self.uq, self.uk_t, self.uv, self.o) + (() if self.g is None else (self.g,))
+        matrices = (self.down, self.uq, self.uk_t, self.uv, self.o)
         return sum(m.numel() for m in matrices) * self.down.element_size() + (self.q_rank + self.kv_rank) * 4
 
     def workspace_elements_per_token(self) -> int:
         return (self.down_rows + self.q_rank + self.h * (self.dim + self.rot) + 2 * self.h * self.d
-                + (3 if self.wide_gate else 1) * self.h * self.vdim + self.hidden)
+                + (2 if self.wide_gate else 1) * self.h * self.vdim + self.hidden)
 
     # -- forward --------------------------------------------------------------- #
     def forward(self, x, batch, cache):
@@ -188,10 +188,8 @@ class LatentAttention(Mixer):
         if self.has_gate:
             kernels.sigmoid_scale_heads(values, down[:, self.g_col0 :], heads=self.h)
         if self.wide_gate:
-            gate = gemm.linear(x, self.g, space.get("latent_gate", rows, self.h * self.vdim, x.dtype), batch.fault)
-            gemm.flush()
             values = kernels.gated_norm(values, space.get("latent_gated", rows, self.h * self.vdim, x.dtype),
-                                        group=self.h * self.vdim, gate=gate, act=kernels.GATE_SIGMOID, norm=False)
+                                        group=self.h * self.vdim, gate=down[:, self.g_col0 :], act=kernels.GATE_SIGMOID, norm=False)
         return gemm.linear(values, self.o, space.get("latent_out", rows, self.hidden, x.dtype), batch.fault)
 
     def _attend(self, q, pages, out, batch, group) -> None:
