@@ -341,6 +341,35 @@ __global__ void layernorm_kernel(const T* __restrict__ x, float* __restrict__ re
   }
 }
 
+// ------------------------------------------------------------ a sigmoid gate, entry by entry
+// out[t, c] = rows[t, c] * sigmoid(gate[t, c]), float32 arithmetic, one rounding; `gate` may be a view of some
+// columns of wider rows (gate_stride).  kVector: eight entries (16 bytes of bfloat16) a thread and step.
+template <typename T, bool kVector>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ rows, const T* __restrict__ gate, int gate_stride,
+                                    T* __restrict__ out, int tokens, int width) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int kStep = kVector ? 8 : 1;
+  const size_t per_row = static_cast<size_t>(width / kStep);
+  const size_t total = static_cast<size_t>(tokens) * per_row;
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = idx / per_row;
+    const int c = static_cast<int>(idx - t * per_row) * kStep;
+    if constexpr (kVector) {
+      float v[8], g[8];
+      load8(rows + t * width + c, v);
+      load8(gate + t * gate_stride + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] / (1.0f + expf(-g[i]));
+      store8(out + t * width + c, v);
+    } else {
+      const float g = to_float(gate[t * gate_stride + c]);
+      out[t * width + c] = from_float<T>(to_float(rows[t * width + c]) / (1.0f + expf(-g)));
+    }
+  }
+}
+
 // ---------------------------------------------------------------- SiLU * up
 // gate_up is [rows, 2 * inter] with the gate in columns [0, inter) and up in
 // [inter, 2 * inter); out[r, c] = silu(gate) * up with silu(z) = z * sigmoid(z), in float32.
@@ -532,6 +561,23 @@ int rl_layernorm(int dtype, const void* x, float* residual, const float* weight,
     return rl::launch_kernel(kernel, dim3(rows), dim3(threads), smem, stream, pdl != 0,
                              static_cast<const scalar_t*>(x), residual, weight, bias, static_cast<scalar_t*>(out),
                              row_index, hidden, eps, res_scale, store, gain);
+  });
+  return 0;
+}
+
+int rl_sigmoid_gate(int dtype, const void* rows, const void* gate, int gate_stride, void* out, int tokens, int width,
+                    int pdl, cudaStream_t stream) {
+  if (tokens == 0 || width == 0) return 0;
+  if (width < 0 || gate_stride < width) return static_cast<int>(cudaErrorInvalidValue);
+  const bool vector = width % 8 == 0 && gate_stride % 8 == 0 && rl::aligned16(rows) && rl::aligned16(gate) && rl::aligned16(out);
+  const size_t total = static_cast<size_t>(tokens) * (vector ? width / 8 : width);
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  RL_DISPATCH_DTYPE(dtype, {
+    auto kernel = vector ? rl::sigmoid_gate_kernel<scalar_t, true> : rl::sigmoid_gate_kernel<scalar_t, false>;
+    return rl::launch_kernel(kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, pdl != 0,
+                             static_cast<const scalar_t*>(rows), static_cast<const scalar_t*>(gate), gate_stride,
+                             static_cast<scalar_t*>(out), tokens, width);
   });
   return 0;
 }

@@ -19,6 +19,8 @@
 //                     scales the expert's input, and W (w h) = w (W h).  With glu_limit > 0 the unit is the
 //                     clamped one: g' = min(g, limit), u' = clamp(u, +-limit), out = g' sigmoid(alpha g') (u' + 1).
 //   rl_moe_combine    out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t]), j in order, float32 sums.
+//   rl_moe_combine_layernorm  the same sum, and at once the layer norm that closes it in an arrangement with the norm
+//                     behind the sum: stream[t] <- LN(res_scale * stream[t] + sum), out[t] its rounding.
 // A row's result does not depend on its tile's other rows or on the order in which the pairs of an
 // expert were laid out: the inner sums run over k in a fixed order per row.
 //
@@ -709,6 +711,48 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T
   }
 }
 
+// ------------------------------------------------------------------ combine, and the layer norm behind the sum
+// One block per token.  s = sum_j (w_j *) y_j as in moe_combine_kernel (an identity expert's y_j is the token's own
+// row), r = res_scale * stream + s, n = (r - mean r) * rsqrt(var r + eps) * ln_weight + ln_bias with the variance
+// as the mean of squared deviations; the stream takes n, out its rounding.  The row waits in shared memory between
+// the passes; the sums run down the block's fixed tree.
+template <typename T>
+__global__ void moe_combine_layernorm_kernel(const float* __restrict__ y, int top, const float* __restrict__ weights,
+                                             const int* __restrict__ ids, int experts, const T* __restrict__ x,
+                                             int x_stride, float* __restrict__ stream, float res_scale,
+                                             const float* __restrict__ ln_weight, const float* __restrict__ ln_bias,
+                                             float eps, T* __restrict__ out, int hidden) {
+  extern __shared__ float combine_row[];
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const long long t = blockIdx.x;
+  pdl_wait();
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float own = ids ? to_float(x[t * x_stride + c]) : 0.0f;
+    float s = 0.0f;
+    for (int j = 0; j < top; ++j) {
+      const float v = (ids && ids[t * top + j] >= experts) ? own : y[(t * top + j) * hidden + c];
+      s = weights ? fmaf(weights[t * top + j], v, s) : s + v;
+    }
+    const float r = fmaf(res_scale, stream[t * hidden + c], s);
+    combine_row[c] = r;
+    sum += r;
+  }
+  const float mean = block_sum(sum, scratch) / static_cast<float>(hidden);
+  float dev = 0.0f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float d = combine_row[c] - mean;
+    dev += d * d;
+  }
+  const float inv = rsqrtf(block_sum(dev, scratch) / static_cast<float>(hidden) + eps);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float n = (combine_row[c] - mean) * inv * ln_weight[c] + (ln_bias ? ln_bias[c] : 0.0f);
+    stream[t * hidden + c] = n;
+    out[t * hidden + c] = from_float<T>(n);
+  }
+}
+
 }  // namespace rl
 
 extern "C" {
@@ -840,6 +884,32 @@ int rl_moe_combine(int dtype, const float* y, int top, const void* shared, const
                              pdl != 0, y, top, static_cast<const scalar_t*>(shared), gate, gate_stride,
                              static_cast<scalar_t*>(out), tokens, hidden, weights, ids, experts,
                              static_cast<const scalar_t*>(x), x_stride);
+  });
+  return 0;
+}
+
+// The sum over a token's choices and the layer norm that closes it: stream (float32, [tokens, hidden]) is read and
+// replaced, out is its rounding.  ids with x as for rl_moe_combine.
+int rl_moe_combine_layernorm(int dtype, const float* y, int top, const float* weights, const int* ids, int experts,
+                             const void* x, int x_stride, float* stream, float res_scale, const float* ln_weight,
+                             const float* ln_bias, float eps, void* out, int tokens, int hidden, int pdl,
+                             cudaStream_t stream_handle) {
+  if (tokens == 0) return 0;
+  const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+  if (hidden < 1 || top < 1 || stream == nullptr || ln_weight == nullptr || (ids != nullptr && x == nullptr) ||
+      smem > 200 * 1024)
+    return static_cast<int>(cudaErrorInvalidValue);
+  int threads = 128;
+  while (threads < 1024 && threads * 4 < hidden) threads *= 2;
+  RL_DISPATCH_DTYPE(dtype, {
+    auto kernel = rl::moe_combine_layernorm_kernel<scalar_t>;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    return rl::launch_kernel(kernel, dim3(tokens), dim3(threads), smem, stream_handle, pdl != 0, y, top, weights, ids,
+                             experts, static_cast<const scalar_t*>(x), x_stride, stream, res_scale, ln_weight, ln_bias,
+                             eps, static_cast<scalar_t*>(out), hidden);
   });
   return 0;
 }

@@ -494,14 +494,32 @@ __global__ void rope_unit_write_kernel(const RopeUnitArgs a) {
 // for k.  Then the first `rotary` entries of every q and k head rotate by halves (entry i with i + rotary / 2, angle
 // position * inv_freq[i], sine and cosine formed here in float32), q goes to q_out and k, v into the pages.
 // One block per token; the sums run down the block's fixed tree, so a token's result does not depend on the step.
-// All arithmetic float32, one rounding at the store.  kv_dest null: the row holds queries only.
+// All arithmetic float32, one rounding at the store.  kv_dest null: the row holds queries only.  Columns of the row
+// behind the heads (a gate's, brought along by the same product) are not read.
+// Sixteen bytes a thread and step: head sizes, row widths and addresses are multiples of eight elements (heads are
+// laid out in multiples of 16).  A thread takes eight neighbouring entries at a time; q and k pass through shared
+// memory as float32 (a rotation's partner lies half the rotated width away, in another thread's eight), v goes
+// straight to its page.  Which thread adds which entries depends on the sizes alone.
+__device__ __forceinline__ void store8_as(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8_as(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
 template <typename T>
-__global__ void row_norm_rope_write_kernel(const T* __restrict__ qkv, int row_width, const float* __restrict__ q_weight,
-                                           const float* __restrict__ k_weight, const float* __restrict__ inv_freq,
-                                           const int* __restrict__ positions, const int* __restrict__ kv_dest,
-                                           T* __restrict__ q_out, T* __restrict__ cache, int hq, int hkv, int d,
-                                           int rotary, int q_count, int k_count, float eps, int page_size,
-                                           int num_pages, int* __restrict__ fault) {
+__global__ void row_norm_rope_write_vec_kernel(const T* __restrict__ qkv, int row_width, const float* __restrict__ q_weight,
+                                               const float* __restrict__ k_weight, const float* __restrict__ inv_freq,
+                                               const int* __restrict__ positions, const int* __restrict__ kv_dest,
+                                               T* __restrict__ q_out, T* __restrict__ cache, int hq, int hkv, int d,
+                                               int rotary, int q_count, int k_count, float eps, int page_size,
+                                               int num_pages, int* __restrict__ fault) {
+  extern __shared__ __align__(16) float row_f32[];      // [hq * d] q, then [hkv * d] k
   __shared__ float scratch[32];
   __shared__ float cs[kMaxHeadDim / 2], sn[kMaxHeadDim / 2];
   pdl_trigger();
@@ -510,55 +528,65 @@ __global__ void row_norm_rope_write_kernel(const T* __restrict__ qkv, int row_wi
   const float pos = static_cast<float>(positions[t]);
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &sn[i], &cs[i]);
   const T* row = qkv + static_cast<size_t>(t) * row_width;
-  const int q_width = hq * d, k_width = hkv * d;
+  const int q_width = hq * d, k_width = kv_dest ? hkv * d : 0;
+  int page = 0, offset = 0;
+  bool bad_page = false;
+  if (kv_dest) {
+    const int dest = kv_dest[t];
+    page = dest / page_size;
+    offset = dest - page * page_size;
+    bad_page = dest < 0 || page >= num_pages;
+  }
   pdl_wait();
   float sum_q = 0.0f, sum_k = 0.0f;
-  for (int i = threadIdx.x; i < q_width; i += blockDim.x) {
-    const float v = to_float(row[i]);
-    sum_q += v * v;
-  }
-  if (kv_dest) {
-    for (int i = threadIdx.x; i < k_width; i += blockDim.x) {
-      const float v = to_float(row[q_width + i]);
-      sum_k += v * v;
+  const int chunks = (q_width + 2 * k_width) >> 3;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const int at = c << 3;
+    float v[8];
+    load8(row + at, v);
+    if (at < q_width + k_width) {
+      store8_as(row_f32 + at, v);
+      float sq = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += v[e] * v[e];
+      if (at < q_width) sum_q += sq; else sum_k += sq;
+    } else if (!bad_page) {
+      const int idx = at - q_width - k_width, head = idx / d, i = idx - head * d;
+      store8_as(cache + (((static_cast<size_t>(page) * 2 + 1) * hkv + head) * page_size + offset) * d + i, v);
     }
   }
-  sum_q = block_sum(sum_q, scratch);      // (its barriers also publish the sines and cosines)
-  const float inv_q = rsqrtf(sum_q / static_cast<float>(q_count) + eps);
-  T* qo = q_out + static_cast<size_t>(t) * q_width;
-  for (int idx = threadIdx.x; idx < q_width; idx += blockDim.x) {
-    const int i = idx % d;
-    float v = to_float(row[idx]) * inv_q * q_weight[idx];
-    if (i < rotary) {
-      const int other_at = i < half ? idx + half : idx - half;
-      const float other = to_float(row[other_at]) * inv_q * q_weight[other_at];
-      const int pair = i < half ? i : i - half;
-      v = i < half ? v * cs[pair] - other * sn[pair] : v * cs[pair] + other * sn[pair];
-    }
-    qo[idx] = from_float<T>(v);
-  }
-  if (!kv_dest) return;
+  sum_q = block_sum(sum_q, scratch);      // (its barriers also publish the row and the sines and cosines)
   sum_k = block_sum(sum_k, scratch);
-  const float inv_k = rsqrtf(sum_k / static_cast<float>(k_count) + eps);
-  const int dest = kv_dest[t];
-  const int page = dest / page_size, offset = dest - page * page_size;
-  if (dest < 0 || page >= num_pages) {
-    if (threadIdx.x == 0) atomicOr(fault, kFaultPageId);
-    return;
-  }
-  const T* kr = row + q_width;
-  const T* vr = kr + k_width;
-  for (int idx = threadIdx.x; idx < k_width; idx += blockDim.x) {
-    const int head = idx / d, i = idx - head * d;
-    float v = to_float(kr[idx]) * inv_k * k_weight[idx];
-    if (i < rotary) {
-      const int other_at = i < half ? idx + half : idx - half;
-      const float other = to_float(kr[other_at]) * inv_k * k_weight[other_at];
-      const int pair = i < half ? i : i - half;
-      v = i < half ? v * cs[pair] - other * sn[pair] : v * cs[pair] + other * sn[pair];
+  const float inv_q = rsqrtf(sum_q / static_cast<float>(q_count) + eps);
+  const float inv_k = rsqrtf(sum_k / static_cast<float>(max(k_count, 1)) + eps);
+  if (bad_page && threadIdx.x == 0) atomicOr(fault, kFaultPageId);
+  const int qk_chunks = (q_width + k_width) >> 3;
+  for (int c = threadIdx.x; c < qk_chunks; c += blockDim.x) {
+    const int at = c << 3;
+    const bool is_q = at < q_width;
+    const int idx = is_q ? at : at - q_width;
+    const float* w = is_q ? q_weight : k_weight;
+    const float* src = row_f32 + (is_q ? 0 : q_width);
+    const float inv = is_q ? inv_q : inv_k;
+    const int head = idx / d, i0 = idx - head * d;
+    float wv[8], v[8];
+    load8(w + idx, wv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int i = i0 + e;
+      v[e] = src[idx + e] * inv * wv[e];
+      if (i < rotary) {
+        const int other_at = i < half ? idx + e + half : idx + e - half;
+        const float other = src[other_at] * inv * w[other_at];
+        const int pair = i < half ? i : i - half;
+        v[e] = i < half ? v[e] * cs[pair] - other * sn[pair] : v[e] * cs[pair] + other * sn[pair];
+      }
     }
-    cache[(((static_cast<size_t>(page) * 2) * hkv + head) * page_size + offset) * d + i] = from_float<T>(v);
-    cache[(((static_cast<size_t>(page) * 2 + 1) * hkv + head) * page_size + offset) * d + i] = vr[idx];
+    if (is_q) {
+      store8_as(q_out + static_cast<size_t>(t) * q_width + idx, v);
+    } else if (!bad_page) {
+      store8_as(cache + (((static_cast<size_t>(page) * 2) * hkv + head) * page_size + offset) * d + i0, v);
+    }
   }
 }
 
@@ -575,13 +603,26 @@ extern "C" int rl_row_norm_rope_write(int dtype, const void* qkv, int row_width,
       (kv_dest != nullptr && (hkv <= 0 || k_count < 1 || k_weight == nullptr || cache == nullptr || page_size <= 0)) ||
       row_width < (kv_dest ? (hq + 2 * hkv) * d : hq * d))
     return static_cast<int>(cudaErrorInvalidValue);
-  RL_DISPATCH_DTYPE(dtype, {
-    return rl::launch_kernel(rl::row_norm_rope_write_kernel<scalar_t>, dim3(tokens), dim3(256), 0, stream, pdl != 0,
-                             static_cast<const scalar_t*>(qkv), row_width, q_weight, k_weight, inv_freq, positions,
-                             kv_dest, static_cast<scalar_t*>(q_out), static_cast<scalar_t*>(cache), hq, hkv, d, rotary,
-                             q_count, k_count, eps, page_size, num_pages, fault);
-  });
-  return 0;
+  const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const int staged = (hq + (kv_dest ? hkv : 0)) * d;
+  if (d % 8 == 0 && row_width % 8 == 0 && aligned(qkv) && aligned(q_out) && aligned(cache) && aligned(q_weight) &&
+      aligned(k_weight) && staged * sizeof(float) <= 200 * 1024) {
+    const size_t smem = static_cast<size_t>(staged) * sizeof(float);
+    int threads = ((hq + (kv_dest ? 2 * hkv : 0)) * d / 8 + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+    RL_DISPATCH_DTYPE(dtype, {
+      auto kernel = rl::row_norm_rope_write_vec_kernel<scalar_t>;
+      if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+      }
+      return rl::launch_kernel(kernel, dim3(tokens), dim3(threads), smem, stream, pdl != 0,
+                               static_cast<const scalar_t*>(qkv), row_width, q_weight, k_weight, inv_freq, positions,
+                               kv_dest, static_cast<scalar_t*>(q_out), static_cast<scalar_t*>(cache), hq, hkv, d, rotary,
+                               q_count, k_count, eps, page_size, num_pages, fault);
+    });
+  }
+  return static_cast<int>(cudaErrorInvalidValue);      // sizes or addresses that are no multiples of 16 bytes
 }
 
 extern "C" int rl_rope_unit_write(int dtype, const float* in, int in_stride, const float* inv_freq,

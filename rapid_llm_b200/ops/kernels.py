@@ -124,6 +124,7 @@ def core() -> ctypes.CDLL:
             c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p,
         ]
+        lib.rl_sigmoid_gate.argtypes = [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rl_silu_mul.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rl_clamped_glu.argtypes = [c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]
         lib.rl_rope_unit_write.argtypes = [
@@ -152,7 +153,7 @@ def core() -> ctypes.CDLL:
         ]
         for name in (
             "rl_embedding", "rl_embedding_sum", "rl_scatter_rows", "rl_add_rmsnorm", "rl_silu_mul", "rl_to_float", "rl_clamped_glu",
-            "rl_rope_unit_write", "rl_layernorm", "rl_row_norm_rope_write",
+            "rl_rope_unit_write", "rl_layernorm", "rl_row_norm_rope_write", "rl_sigmoid_gate",
             "rl_qk_norm_rope_write", "rl_attention_generic", "rl_gemm_f32", "rl_sample",
         ):
             getattr(lib, name).restype = c_int
@@ -362,6 +363,18 @@ def row_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: in
         int(k_count), float(eps), page_size, num_pages, _ptr(fault), int(PDL), _stream()),
         f"row_norm_rope_write(head_dim={head_dim})")
     return q_out
+
+
+def sigmoid_gate(rows: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = rows * sigmoid(gate)`` entry by entry (float32 arithmetic); ``gate`` may be a view of some columns of
+    wider rows."""
+    _need_cuda(rows, gate, out)
+    _contig("rows", rows), _contig("out", out)
+    if gate.shape != rows.shape or out.shape != rows.shape or gate.dtype != rows.dtype or out.dtype != rows.dtype:
+        raise KernelError("sigmoid_gate: shapes or dtypes do not agree")
+    _check(core().rl_sigmoid_gate(dtype_tag(rows.dtype), _ptr(rows), _ptr(gate), _row_stride("gate", gate), _ptr(out),
+                                  rows.shape[0], rows.shape[1], int(PDL), _stream()), "sigmoid_gate")
+    return out
 
 
 def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
@@ -1421,7 +1434,10 @@ def moe_lib() -> ctypes.CDLL:
                                           c_void_p]
         lib.rl_moe_combine.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
-        for name in ("rl_router_topk", "rl_moe_plan", "rl_grouped_linear", "rl_moe_combine", "rl_moe_tile_rows"):
+        lib.rl_moe_combine_layernorm.argtypes = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                                 c_float, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p]
+        for name in ("rl_router_topk", "rl_moe_plan", "rl_grouped_linear", "rl_moe_combine", "rl_moe_tile_rows",
+                     "rl_moe_combine_layernorm"):
             getattr(lib, name).restype = c_int
         _MOE_LIB = lib
     return _MOE_LIB
@@ -1546,6 +1562,28 @@ def moe_combine(y: torch.Tensor, top: int, out: torch.Tensor, shared: torch.Tens
                                     0 if gate is None else _row_stride("gate", gate), _ptr(out), tokens, hidden,
                                     _ptr(weights), _ptr(ids), int(experts), _ptr(x),
                                     0 if x is None else _row_stride("x", x), int(PDL), _stream()), "moe_combine")
+    return out
+
+
+def moe_combine_layernorm(y: torch.Tensor, top: int, stream: torch.Tensor, ln_weight: torch.Tensor,
+                          ln_bias: torch.Tensor | None, out: torch.Tensor, eps: float, *, stream_scale: float = 1.0,
+                          weights: torch.Tensor | None = None, ids: torch.Tensor | None = None, experts: int = 0,
+                          x: torch.Tensor | None = None) -> torch.Tensor:
+    """The sum of :func:`moe_combine` (weights, identity experts) and the layer norm that closes it, in one pass:
+    ``stream[t] <- LN(stream_scale * stream[t] + sum_j w_j y_j)`` (float32, in place), ``out`` its rounding."""
+    _need_cuda(y, stream, ln_weight, ln_bias, out, weights, ids, x)
+    for name, tensor in (("y", y), ("stream", stream), ("ln_weight", ln_weight), ("ln_bias", ln_bias), ("weights", weights)):
+        _expect(name, tensor, torch.float32), _contig(name, tensor)
+    _expect("ids", ids, torch.int32), _contig("ids", ids), _contig("out", out)
+    tokens, hidden = out.shape
+    if (y.shape != (tokens * top, hidden) or stream.shape != out.shape or ln_weight.numel() != hidden
+            or (ln_bias is not None and ln_bias.numel() != hidden) or (weights is not None and weights.numel() != tokens * top)
+            or (ids is None) != (x is None) or (ids is not None and (ids.numel() != tokens * top or x.shape != out.shape or x.dtype != out.dtype))):
+        raise KernelError("moe_combine_layernorm: shapes or dtypes do not agree")
+    _check(moe_lib().rl_moe_combine_layernorm(
+        dtype_tag(out.dtype), _ptr(y), int(top), _ptr(weights), _ptr(ids), int(experts), _ptr(x),
+        0 if x is None else _row_stride("x", x), _ptr(stream), float(stream_scale), _ptr(ln_weight), _ptr(ln_bias), float(eps),
+        _ptr(out), tokens, hidden, int(PDL), _stream()), "moe_combine_layernorm")
     return out
 
 

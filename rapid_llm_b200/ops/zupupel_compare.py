@@ -141,11 +141,17 @@ def kernel_figures(width: int, hbm_gbs: float) -> dict:
               lambda: kernels.moe_combine(each, TOP, combined, weights=weights.view(-1), ids=ids, experts=EXPERTS, x=x))
         timed("moe_combine, weights (like kernel)", tokens, entries, pairs * width * 4 + tokens * width * 2,
               lambda: kernels.moe_combine(each, TOP, combined, weights=weights.view(-1)))
-        # -- the gate over the heads side by side (the same kernel serves Mezadra's linear attention)
+        timed("moe_combine_layernorm: the sum, the stream and the norm behind them", tokens, entries,
+              pairs * width * 4 + tokens * width * 12,
+              lambda: kernels.moe_combine_layernorm(each, TOP, stream, weight, bias, combined, 1e-6, stream_scale=2.0,
+                                                    weights=weights.view(-1), ids=ids.view(-1), experts=EXPERTS, x=x))
+        # -- the gate over the heads side by side, entry by entry, beside the gate of one number a head (Basitar's)
         attended, gate = bf(tokens, heads * d), bf(tokens, heads * d)
         gated = torch.empty_like(attended)
-        timed("gated_norm, sigmoid gate over all heads, no norm", tokens, entries, tokens * heads * d * 6,
-              lambda: kernels.gated_norm(attended, gated, group=heads * d, gate=gate, act=kernels.GATE_SIGMOID, norm=False))
+        timed("sigmoid_gate, entry by entry", tokens, entries, tokens * heads * d * 6,
+              lambda: kernels.sigmoid_gate(attended, gate, gated))
+        timed("sigmoid_scale_heads (like kernel)", tokens, entries, tokens * heads * d * 4,
+              lambda: kernels.sigmoid_scale_heads(attended, gate, heads=heads))
     assert int(fault.item()) == 0, "a kernel reported a fault"
     return out
 

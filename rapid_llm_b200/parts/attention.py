@@ -406,7 +406,7 @@ class GQAAttention(Mixer):
         return self.qkv.shape[0] + 2 * self.hq * self.d + self.hidden + gate      # qkv, q, attended, projected
 
     def uses_libraries(self) -> set[str]:
-        found = {"recurrent"} if self.gate or self.float_prelude else set()
+        found = {"recurrent"} if self.float_prelude else set()
         if self.dtype == torch.bfloat16:
             from ..ops.build import attention_library
             found |= {"gemm", attention_library(self.d)}
@@ -443,8 +443,7 @@ class GQAAttention(Mixer):
                 gate = batch.workspace.get("attn_gate", rows, self.hq * self.d, x.dtype)
                 gemm.linear(x, self.g, gate, batch.fault)
             gated = batch.workspace.get("attn_gated", rows, self.hq * self.d, x.dtype)
-            attended = kernels.gated_norm(attended, gated, group=self.hq * self.d, gate=gate,
-                                          act=kernels.GATE_SIGMOID, norm=False)
+            attended = kernels.sigmoid_gate(attended, gate, gated)
         out = batch.workspace.get("attn_proj", rows, self.hidden, x.dtype)
         return gemm.linear(attended, self.o, out, batch.fault, then_norm=then_norm, defer=batch.defer_products)
 

@@ -249,6 +249,14 @@ class SandwichBlock(PreNormBlock):
         return self._close(wide, self.feed_forward_out_norm, residual, batch, after), residual
 
 
+class ClosingNorm:
+    """The norm behind a sum, ``stream <- norm(alpha * stream + y)``, as a :class:`PostNormBlock` offers it to a
+    feed-forward whose last kernel can take it along (class flag ``closes_sums``)."""
+
+    def __init__(self, norm, residual: torch.Tensor, alpha: float) -> None:
+        self.norm, self.residual, self.alpha = norm, residual, alpha
+
+
 @BLOCKS.register("postnorm")
 class PostNormBlock(PreNormBlock):
     """The norm behind the sum: ``h <- Norm1(alpha * h + Mixer(h)); h <- Norm2(alpha * h + FeedForward(h))``.
@@ -268,6 +276,8 @@ class PostNormBlock(PreNormBlock):
         for norm in (self.mixer_norm, self.feed_forward_norm):
             if norm is not None and not hasattr(norm, "post_join"):
                 raise ValueError("the postnorm arrangement needs norms that can close a sum (kind 'layernorm')")
+        self._closes = (self.feed_forward is not None and getattr(self.feed_forward, "closes_sums", False)
+                        and getattr(self.feed_forward, "shared", None) is None and getattr(self.feed_forward_norm, "gain", 1.0) == 1.0)
 
     def leading_norm(self):
         return None
@@ -282,7 +292,10 @@ class PostNormBlock(PreNormBlock):
         gemm.flush()
         x = self.mixer_norm.post_join(mixed, residual, self.alpha, batch)
         if self.feed_forward is not None:
-            wide = self.feed_forward.forward(x, batch)
-            gemm.flush()
-            x = self.feed_forward_norm.post_join(wide, residual, self.alpha, batch)
+            if self._closes:      # the feed-forward's last kernel takes the sum with the stream and its norm along
+                x = self.feed_forward.forward(x, batch, closing=ClosingNorm(self.feed_forward_norm, residual, self.alpha))
+            else:
+                wide = self.feed_forward.forward(x, batch)
+                gemm.flush()
+                x = self.feed_forward_norm.post_join(wide, residual, self.alpha, batch)
         return x, residual

@@ -99,7 +99,7 @@ class LatentAttention(Mixer):
         return self._items if self.dtype == torch.bfloat16 and not self.wide_row else None
 
     def uses_libraries(self) -> set[str]:
-        found = {"latent"} | ({"recurrent"} if self.wide_gate else set())
+        found = {"latent"}
         if self.dtype == torch.bfloat16:
             from ..ops.build import attention_library
             found |= {"gemm"} | (set() if self.wide_row else {attention_library(self.d)})
@@ -188,8 +188,7 @@ class LatentAttention(Mixer):
         if self.has_gate:
             kernels.sigmoid_scale_heads(values, down[:, self.g_col0 :], heads=self.h)
         if self.wide_gate:
-            values = kernels.gated_norm(values, space.get("latent_gated", rows, self.h * self.vdim, x.dtype),
-                                        group=self.h * self.vdim, gate=down[:, self.g_col0 :], act=kernels.GATE_SIGMOID, norm=False)
+            values = kernels.sigmoid_gate(values, down[:, self.g_col0 :], space.get("latent_gated", rows, self.h * self.vdim, x.dtype))
         return gemm.linear(values, self.o, space.get("latent_out", rows, self.hidden, x.dtype), batch.fault)
 
     def _attend(self, q, pages, out, batch, group) -> None:

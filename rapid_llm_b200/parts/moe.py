@@ -152,7 +152,12 @@ class RoutedExperts(FeedForward):
         return {"moe"} | ({"gemm"} if self.dtype == torch.bfloat16 else set())
 
     # -- forward ------------------------------------------------------------ #
-    def forward(self, x, batch):
+    # An arrangement whose norm stands BEHIND the sum (``x <- Norm(alpha x + FeedForward(x))``) may hand that norm to
+    # ``forward`` as ``closing``: the last kernel then sums a token's experts, forms the sum with the stream and norms it
+    # in one pass, and ``forward`` returns the new stream's rounding instead of the feed-forward's own result.
+    closes_sums = True
+
+    def forward(self, x, batch, closing=None):
         space, i32, f32 = batch.workspace, torch.int32, torch.float32
         tokens, top, experts = x.shape[0], self.top, self.experts
         pairs = tokens * top
@@ -175,6 +180,14 @@ class RoutedExperts(FeedForward):
         each = space.get("moe_each", tokens, top * self.hidden, f32).view(pairs, self.hidden)
         kernels.grouped_linear(act, self.down, order, meta, top=top, by_token=False, max_tiles=max_tiles, out_y=each, wide=wide)
         shared = None if self.shared is None else self.shared.forward(x, batch)
+        if closing is not None and shared is None and hasattr(closing.norm, "bias") and closing.norm.gain == 1.0:
+            out = space.get("stream_rows", tokens, self.hidden, x.dtype)
+            return kernels.moe_combine_layernorm(
+                each, top, closing.residual, closing.norm.weight, closing.norm.bias, out, closing.norm.eps,
+                stream_scale=closing.alpha, weights=None if self.scale_input else weights.view(-1),
+                ids=ids.view(-1) if self.identity else None, experts=experts, x=x if self.identity else None)
+        if closing is not None:
+            raise ValueError("this feed-forward closes a sum only with a layer norm and without a shared expert")
         out = space.get("moe_out", tokens, self.hidden, x.dtype)
         # pairs whose id lies behind the experts with tensors (identity experts) are in no tile of the plan: the sum
         # takes the token's own row for them

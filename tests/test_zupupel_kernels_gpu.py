@@ -251,3 +251,48 @@ def test_rows_wider_than_the_tensor_core_tiles(d, dtype):
     want = torch.einsum("hij,jd->ihd", torch.softmax(scores, -1), kf).reshape(tokens, heads * d)
     bound = {"rtol": 1e-4, "atol": 1e-5} if dtype == torch.float32 else {"rtol": 2e-2, "atol": 2e-2}
     torch.testing.assert_close(out.double().cpu(), want, **bound)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,stride", [(64, 64), (64, 200), (50, 50), (30, 77)])
+def test_a_sigmoid_gate_entry_by_entry(width, stride, dtype):
+    from rapid_llm_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(width + stride)
+    rows = torch.randn(19, width, generator=g).to(dtype).to(DEVICE)
+    wide = (3 * torch.randn(19, stride, generator=g)).to(dtype).to(DEVICE)
+    gate = wide[:, stride - width :]                      # a view of the last columns of wider rows
+    out = torch.empty_like(rows)
+    kernels.sigmoid_gate(rows, gate, out)
+    want = rows.float() * torch.sigmoid(gate.float())
+    bound = {"rtol": 1e-6, "atol": 1e-6} if dtype == torch.float32 else {"rtol": 1e-2, "atol": 1e-2}
+    torch.testing.assert_close(out.float(), want, **bound)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,top,hidden,identity", [(33, 3, 64, True), (5, 1, 50, False), (70, 4, 1032, True)])
+def test_the_sum_over_a_tokens_experts_with_the_norm_behind_it(tokens, top, hidden, identity, dtype):
+    """``stream <- LN(alpha * stream + sum_j w_j y_j)`` in one kernel equals the sum's kernel followed by the norm's,
+    and the plain formula; identity experts' rows of ``y`` are never read."""
+    from rapid_llm_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(tokens)
+    experts = 5
+    y = torch.randn(tokens * top, hidden, generator=g).to(DEVICE)
+    ids = torch.randint(0, experts + (3 if identity else 0), (tokens, top), generator=g).to(torch.int32).to(DEVICE)
+    if identity:
+        y[(ids.view(-1) >= experts)] = float("nan")
+    weights = torch.rand(tokens, top, generator=g).to(DEVICE)
+    x = torch.randn(tokens, hidden, generator=g).to(dtype).to(DEVICE)
+    stream = (2 * torch.randn(tokens, hidden, generator=g) + 0.5).to(DEVICE)
+    ln_w, ln_b = (1 + 0.2 * torch.randn(hidden, generator=g)).to(DEVICE), (0.3 * torch.randn(hidden, generator=g)).to(DEVICE)
+    before, out = stream.clone(), torch.empty(tokens, hidden, dtype=dtype, device=DEVICE)
+    kernels.moe_combine_layernorm(y, top, stream, ln_w, ln_b, out, 1e-5, stream_scale=1.5, weights=weights.view(-1),
+                                  ids=ids.view(-1) if identity else None, experts=experts, x=x if identity else None)
+    rows = y.view(tokens, top, hidden).double()
+    if identity:
+        rows = torch.where((ids >= experts)[:, :, None], x.double()[:, None, :], rows)
+    total = (weights.double()[:, :, None] * rows).sum(1)
+    want = torch.nn.functional.layer_norm(1.5 * before.double() + total, (hidden,), ln_w.double(), ln_b.double(), 1e-5).float()
+    torch.testing.assert_close(stream, want, rtol=2e-5, atol=2e-5)
+    assert torch.equal(out, stream.to(dtype))
