@@ -10,7 +10,7 @@ Random weights, bfloat16, one GPU.  A model of width ``W`` has six layers, ``att
 cache), latent_attention, attention, attention (reads layer 3's cache), latent_attention``, each followed by routed
 experts: ``W / 128`` attention heads of 128 over ``W / 512`` key/value heads, 64 rotated entries, a window of 512
 positions, a gate over the heads; latent attention with 128 plain, 64 rotated and 128 value entries over a latent of
-192 (a cached row of 256 numbers); 16 clamped experts of ``W / 4`` and 4 identity experts in 4 groups of which 2 are
+192 (a cached row of 256 numbers); 16 clamped experts of ``W / 4`` and 8 identity experts in 4 groups of which 2 are
 kept, a token taking two.  Basitar, Mezadra and Qwen3 beside it have six layers of the same width.  Prefill is one
 2,048-token step (best of three, CUDA events around the step function); decode is batch 8 behind 1,024-token prompts,
 replayed from the captured graph (median of 32 steps).  Kernels are timed alone with CUDA events, L2 flushed between
@@ -30,7 +30,7 @@ from .basitar_compare import basitar_raw
 from .mezadra_compare import mezadra_raw
 from .recurrent_compare import PREFILL, _events, model_figures, qwen3_raw
 
-EXPERTS, IDENTITY, TOP, GROUPS, KEEP = 16, 4, 2, 4, 2
+EXPERTS, IDENTITY, TOP, GROUPS, KEEP = 16, 8, 2, 4, 2
 PLAIN, ROT, VDIM, KV_RANK, WINDOW = 128, 64, 128, 192, 512
 
 
@@ -45,7 +45,7 @@ def zupupel_raw(width: int) -> dict:
     order = [("attention", attention), ("attention", {**attention, "kv_from": 0}), ("latent_attention", latent),
              ("attention", attention), ("attention", {**attention, "kv_from": 3}), ("latent_attention", latent)]
     return {"architecture": "Zupupel", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
-            "postln_alpha": 2.0, "logit_scale": 0.5,
+            "postln_alpha": 2.0, "logit_scale": 0.25,
             "layers": [{"type": kind, "mixer": dict(mixer), "mlp": dict(experts)} for kind, mixer in order]}
 
 

@@ -31,7 +31,7 @@ def test_the_model_expects_the_files_tensors(name):
 def test_parts_run_order_and_what_a_layer_keeps_for_its_readers():
     spec = ZupupelConfig.from_dict(CONFIGS["stack"]).to_spec()
     assert [layer.arrangement for layer in spec.layers] == ["postnorm"] * 7
-    assert all(layer.arrangement_params == {"alpha": 3.0} for layer in spec.layers)
+    assert all(layer.arrangement_params == {"alpha": 2.5} for layer in spec.layers)
     assert [layer.mixer.kind for layer in spec.layers] == ["latent_attention", "gqa_attention", "gqa_attention", "gqa_attention",
                                                             "gqa_attention", "latent_attention", "gqa_attention"]
     assert [entry.cache_from for entry in spec.schedule] == [None, None, 1, None, 1, None, 3]
@@ -47,8 +47,8 @@ def test_parts_run_order_and_what_a_layer_keeps_for_its_readers():
     assert (experts["num_experts"], experts["identity_experts"], experts["top_k"], experts["num_groups"], experts["group_keep"],
             experts["weighting"], experts["scale_input"], experts["expert_alpha"]) == (5, 1, 1, 3, 2, "softmax_all", False, 1.702)
     assert spec.layers[2].feed_forward is None
-    assert spec.embedding.params["scale"] == 0.5 and spec.embedding.params["opens_stream"]
-    assert spec.final_norm.kind == "layernorm" and spec.final_norm.params["gain"] == 0.5
+    assert spec.embedding.params["scale"] == 0.6 and spec.embedding.params["opens_stream"]
+    assert spec.final_norm.kind == "layernorm" and spec.final_norm.params["gain"] == 0.4
     model = CausalLM(spec, torch.float32, "cpu")
     needs = model.cache_needs()
     assert [need is not None for need in needs] == [True, True, False, True, False, True, False]
@@ -248,3 +248,20 @@ def test_every_mechanism_moves_the_logits():
         extra[name] = torch.ones(shapes[name], dtype=torch.float64) * 0.1
     assert moved(own_keys, extra) > 0.05
     assert math.isfinite(moved())
+
+
+def test_a_random_model_folder_is_written_and_read_back(tmp_path):
+    """``random-init`` takes the architecture from the file like every other entry point: the folder it writes holds
+    exactly the tensors the model expects, and loads as this architecture."""
+    import json
+
+    from rapid_llm_b200.cli import main
+    from rapid_llm_b200.config import load_config
+    from rapid_llm_b200.weights.safetensors_io import SafetensorsFile
+
+    (tmp_path / "config.json").write_text(json.dumps(CONFIGS["narrow"]))
+    assert main(["random-init", "--config", str(tmp_path / "config.json"), "--out", str(tmp_path / "model"), "--seed", "3"]) == 0
+    assert isinstance(load_config(tmp_path / "model"), ZupupelConfig)
+    written = SafetensorsFile(tmp_path / "model" / "model.safetensors")
+    shapes = {name: written.shape(name) for name in written.keys()}
+    assert shapes == tensor_shapes(CONFIGS["narrow"])

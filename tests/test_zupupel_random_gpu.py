@@ -54,7 +54,7 @@ def draw_config(seed: int) -> dict:
         kv_heads = rng.choice([1, 2, 3, 4])
         dim = rng.choice([8, 12, 16, 32, 64, 128])
         layers.append(attention_layer(heads=kv_heads * rng.choice([1, 2, 4]), kv_heads=kv_heads, dim=dim,
-                                      vdim=rng.choice([8, 16, 24, 64, 128]), window=rng.choice([0, 1, 3, 8, 17, 40]),
+                                      vdim=rng.choice([8, 16, 24, 64, 128]), window=rng.choice([0, 1, 3, 8, 17, 41]),
                                       rot_dims=rng.choice([0, 2, dim // 2, dim]), base=rng.choice([50.0, 1.0e4, 1.0e6]),
                                       scale=rng.uniform(0.1, 0.5), mlp=mlp))
     return make_config(layers, width=rng.choice([32, 40, 48, 64, 72, 96]), vocab=rng.randint(50, 200), eps=rng.choice([1e-6, 1e-5]),

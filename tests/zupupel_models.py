@@ -62,7 +62,7 @@ CONFIGS = {
         attention_layer(heads=6, kv_heads=3, dim=16, vdim=32, window=5, rot_dims=16, kv_from=1, mlp=moe(experts=3, top=2, ff=8, identity=3, groups=3, keep=3)),
         latent_layer(heads=5, dim=8, rot_dim=4, vdim=8, kv_rank=24, base=1.0e4, scale=0.5, mlp=None),
         attention_layer(heads=4, kv_heads=1, dim=32, vdim=16, window=7, rot_dims=4, base=1.0e4, scale=0.2, kv_from=3, mlp=None),
-    ], width=72, vocab=130, alpha=3.0, embedding_scale=0.5, logit_scale=0.5),
+    ], width=72, vocab=130, alpha=2.5, embedding_scale=0.6, logit_scale=0.4),
     # nothing is a multiple of 4 or 8: every kernel's element-by-element path
     "narrow": make_config([
         attention_layer(heads=3, kv_heads=3, dim=10, vdim=6, window=3, rot_dims=6, scale=0.7, mlp=moe(experts=7, top=3, ff=10, identity=2, groups=3, keep=2)),
