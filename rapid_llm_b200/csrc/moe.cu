@@ -161,7 +161,7 @@ router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hi
   if (warp >= kRouterTokens || t0 + warp >= tokens) return;
   const int t = t0 + warp;
   float* s = moe_scores + warp * rows;
-  if (scores_out)
+  if (scores_out && weigh != 2)
     for (int e = lane; e < experts; e += 32) scores_out[static_cast<size_t>(t) * experts + e] = moe_sigmoid(s[e]);
   for (int g = lane; g < gates; g += 32) gate_out[static_cast<size_t>(t) * gates + g] = moe_sigmoid(s[experts + g]);
   __syncwarp();
@@ -182,6 +182,7 @@ router_topk_kernel(const T* x, int x_stride, const float* __restrict__ w, int hi
     for (int e = lane; e < experts; e += 32) {
       const float p = expf(s[e] - largest) / total;
       s[e] = p;                                            // the plain score: what the weights are made of
+      if (scores_out) scores_out[static_cast<size_t>(t) * experts + e] = p;
       choice[e] = p + (correction ? correction[e] : 0.0f);
     }
     __syncwarp();

@@ -1469,7 +1469,8 @@ def router_topk(x: torch.Tensor, weight: torch.Tensor, *, experts: int, top: int
     With ``softmax_all`` the scores are ``s = softmax(z)`` over all ``experts`` rows; the choice is made on
     ``s + correction`` (one float per row) among the rows of the ``keep`` best of ``groups`` equal groups of
     neighbouring rows (a group ranks by its largest corrected score; rows of the other groups count as minus
-    infinity), and the weights are the chosen rows' ``s`` divided by their sum (plus 1e-20)."""
+    infinity), and the weights are the chosen rows' ``s`` divided by their sum (plus 1e-20).  ``scores`` (float32
+    ``[T, experts]``) receives every row's score: the sigmoid of its logit, or its softmax share with ``softmax_all``."""
     _need_cuda(x, weight, ids, weights, gates, scores, bias, correction)
     _expect("bias", bias, torch.float32), _contig("bias", bias)
     _expect("correction", correction, torch.float32), _contig("correction", correction)

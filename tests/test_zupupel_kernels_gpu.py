@@ -133,9 +133,11 @@ def test_the_router_over_all_rows_with_corrections_and_groups(rows, top, groups,
     correction = (0.1 * torch.randn(rows, generator=g)).to(DEVICE)
     ids = torch.empty(tokens, top, dtype=torch.int32, device=DEVICE)
     weights = torch.empty(tokens, top, device=DEVICE)
-    kernels.router_topk(x, w, experts=rows, top=top, ids=ids, weights=weights, softmax_all=True, correction=correction,
-                        groups=groups, keep=keep)
+    all_scores = torch.empty(tokens, rows, device=DEVICE)
+    kernels.router_topk(x, w, experts=rows, top=top, ids=ids, weights=weights, scores=all_scores, softmax_all=True,
+                        correction=correction, groups=groups, keep=keep)
     scores = torch.softmax(x.double() @ w.double().T, dim=-1).cpu()
+    torch.testing.assert_close(all_scores.double().cpu(), scores, rtol=1e-5, atol=1e-7)
     choice = scores + correction.double().cpu()
     per = rows // groups
     best = choice.view(tokens, groups, per).max(-1).values

@@ -87,3 +87,69 @@ def test_a_drawn_configuration_in_mixed_batches(seed, dtype, tmp_path):
     records, peak = mixed(sequences, seed=seed, max_live=3, page=8)
     runner = _runner(folder, config, dtype, peak, page=8, slots=3)
     _check(_replay(runner, records), plain, dtype, f"seed {seed} {dtype}: {config}", True)
+
+
+def draw_large_config(seed: int) -> dict:
+    """Sizes nearer to a real model's: widths of a few hundred, heads of 32 to 128, windows of tens of positions, latents
+    of up to 256, router rows in groups of several."""
+    rng = random.Random(400 + seed)
+    layers = []
+    for _ in range(rng.randint(4, 7)):
+        groups, per = rng.choice([1, 2, 4]), rng.choice([3, 4, 5, 8])
+        rows = groups * per
+        identity, keep = rng.randint(0, rows // 3), rng.randint(1, groups)
+        mlp = None if rng.random() < 0.15 else moe(experts=rows - identity, identity=identity, top=rng.randint(1, min(6, keep * per)),
+                                                   ff=rng.choice([32, 48, 96]), groups=groups, keep=keep, limit=rng.choice([0.5, 2.0]))
+        owners = [i for i, layer in enumerate(layers) if layer["type"] == "attention" and "kv_from" not in layer["mixer"]]
+        if owners and rng.random() < 0.35:
+            owner = rng.choice(owners)
+            mixer = dict(layers[owner]["mixer"])
+            mixer.pop("mask", None)
+            window = rng.choice([0, 24, 56, 100])
+            if window:
+                mixer["mask"] = {"size": window}
+            mixer["kv_from"] = owner
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+            continue
+        if rng.random() < 0.3:
+            layers.append(latent_layer(heads=rng.choice([4, 6, 8]), dim=rng.choice([32, 48, 64]), rot_dim=rng.choice([16, 32]),
+                                       vdim=rng.choice([32, 64]), kv_rank=rng.choice([64, 96, 192, 256]), base=rng.choice([1e4, 2.5e5]),
+                                       scale=rng.uniform(0.08, 0.2), mlp=mlp))
+            continue
+        kv_heads, dim = rng.choice([1, 2, 4]), rng.choice([32, 96, 128])
+        layers.append(attention_layer(heads=kv_heads * rng.choice([1, 2, 4]), kv_heads=kv_heads, dim=dim, vdim=rng.choice([32, 64, 128]),
+                                      window=rng.choice([0, 24, 33, 48]), rot_dims=rng.choice([16, 32, dim]), base=rng.choice([1e4, 1e6]),
+                                      scale=rng.uniform(0.08, 0.2), mlp=mlp))
+    return make_config(layers, width=rng.choice([128, 192, 320]), vocab=rng.randint(300, 900), eps=1e-6, alpha=rng.choice([1.0, 2.0, 4.0]),
+                       embedding_scale=rng.choice([1.0, 2.0]), logit_scale=rng.choice([0.3, 1.0]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(3))
+def test_a_larger_drawn_model_over_hundreds_of_tokens(seed, tmp_path):
+    """Float32, a 700-token request whole, with its tail decoded, in portions of changing size, and mixed with shorter
+    requests on four slots: every row within 5e-5 of the logits' spread (difference with its mean removed, root mean
+    square over the vocabulary), which a key lost far back, a window off by one or a wrong expert would exceed a
+    thousandfold."""
+    import torch
+    from trace_tools import portions, tail_one_by_one, whole
+
+    config = draw_large_config(seed)
+    weights = make_weights(config, seed=500 + seed)
+    folder = write_folder(tmp_path / "model", config, weights, torch.float32)
+    generator = torch.Generator().manual_seed(seed)
+    sequences = {f"r{i}": torch.randint(0, config["vocab"], (n,), generator=generator).tolist() for i, n in enumerate([700, 260, 90, 33, 1])}
+    double = as_double(weights)
+    plain = {rid: forward(config, double, tokens) for rid, tokens in sequences.items()}
+    records, peak = mixed(sequences, seed=seed, max_live=4, page=16)
+    runner = _runner(folder, config, "float32", max(peak, 704), page=16, slots=4)
+    first = sequences["r0"]
+    for label, trace in (("whole", whole("r0", first)), ("tail", tail_one_by_one("r0", first, tail=70)),
+                         ("portions", portions("r0", first, [37, 37, 14, 19, 6, 2, 128, 1, 1, 64])), ("mixed", records)):
+        for rid, by_position in _replay(runner, trace).items():
+            positions = sorted(by_position)
+            got = torch.stack([by_position[p] for p in positions]).double()
+            want = plain[rid][positions]
+            error = got - want
+            share = (error - error.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / want.std()
+            assert float(share.max()) < 5e-5, f"seed {seed} ({label}): request {rid!r}, position {positions[int(share.argmax())]}: {float(share.max()):.2e}"
